@@ -1,0 +1,92 @@
+"""GPU tests of the stage-level entry points (the reference's kernel tables) against the oracle."""
+import numpy as np
+import pytest
+
+from util import assert_close, oracle_np
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(cuda, a):
+    import torch
+
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+@pytest.mark.parametrize("DY", [128, 256, 512, 1024])
+def test_fft_and_ifft_stride_DY(cuda, DY):
+    import torch
+    import turbofno_b200 as t
+
+    S = 150                                   # not a multiple of the signals-per-CTA
+    x, _ = oracle_np.make_inputs_1d(S, 1, 64, DY, seed=DY)
+    x = x[:, 0, :]
+    out = torch.empty((S, 64), dtype=torch.complex64, device=cuda)
+    t.fft_stride_DY(_dev(cuda, x), out, S, DY)
+    spec = np.fft.fft(x.astype(np.complex128), axis=-1)[:, :64]
+    assert_close(out.cpu().numpy(), spec, "fft_stride_DY %d" % DY)
+    back = torch.empty((S, DY), dtype=torch.complex64, device=cuda)
+    t.ifft_stride_DY(_dev(cuda, spec.astype(np.complex64)), back, S, DY)
+    assert_close(back.cpu().numpy(), oracle_np.ifft_pad_1d(spec.astype(np.complex64), DY, scale=False), "ifft_stride_DY %d" % DY)
+
+
+@pytest.mark.parametrize("DX,DY", [(128, 128), (256, 128), (128, 256), (512, 64 * 3)])
+def test_fft_and_ifft_stride_X(cuda, DX, DY):
+    import torch
+    import turbofno_b200 as t
+
+    I = 3
+    rng = np.random.default_rng(DX + DY)
+    x = (rng.uniform(-1, 1, (I, DX, DY)) + 1j * rng.uniform(-1, 1, (I, DX, DY))).astype(np.complex64)
+    out = torch.empty((I, 64, DY), dtype=torch.complex64, device=cuda)
+    t.fft_stride(_dev(cuda, x), out, DY, I * DY, DX)
+    ref = oracle_np.fft_cols_trunc(x)
+    assert_close(out.cpu().numpy(), ref, "fft_stride")
+    back = torch.empty((I, DX, DY), dtype=torch.complex64, device=cuda)
+    t.ifft_stride(_dev(cuda, ref.astype(np.complex64)), back, DY, I * DY, DX)
+    assert_close(back.cpu().numpy(), oracle_np.ifft_cols_pad(ref.astype(np.complex64), DX, scale=False), "ifft_stride")
+
+
+@pytest.mark.parametrize("rows,K,N", [(1, 8, 64), (5, 24, 128), (300, 64, 64), (3, 128, 192)])
+def test_cgemm(cuda, rows, K, N):
+    import torch
+    import turbofno_b200 as t
+
+    M = rows * 64
+    rng = np.random.default_rng(rows + K)
+    A = (rng.standard_normal((K, M)) + 1j * rng.standard_normal((K, M))).astype(np.complex64)      # A[m + k*M]
+    Bm = (rng.standard_normal((N, K)) + 1j * rng.standard_normal((N, K))).astype(np.complex64)     # B[k + n*K]
+    C0 = (rng.standard_normal((N, M)) + 1j * rng.standard_normal((N, M))).astype(np.complex64)
+    alpha, beta = 1 - 1j, -1 + 1j             # the reference drivers' constants
+    C = _dev(cuda, C0)
+    t.cgemm(M, N, K, _dev(cuda, A), _dev(cuda, Bm), C, alpha, beta)
+    ref = alpha * (Bm.astype(np.complex128) @ A.astype(np.complex128)) + beta * C0
+    assert_close(C.cpu().numpy(), ref, "cgemm")
+
+
+@pytest.mark.parametrize("DY", [128, 256])
+def test_partial_fusions(cuda, DY):
+    import torch
+    import turbofno_b200 as t
+
+    B, K, N = 9, 16, 128
+    M = B * 64
+    x, w = oracle_np.make_inputs_1d(B, K, N, DY, seed=DY + 1)
+    xd = _dev(cuda, np.swapaxes(x, 0, 1))     # [K][B][DY]
+    wd = _dev(cuda, w.T)                      # [N][K]
+    spec = oracle_np.spectrum_1d(x)           # [B,K,64]
+    cref = oracle_np.cgemm_modes(spec, w)     # [B,N,64]
+    # fused FFT + CGEMM -> compact C[n][M]
+    C = torch.zeros((N, M), dtype=torch.complex64, device=cuda)
+    t.fused_fft_cgemm(M, N, K, xd, wd, C, DY=DY)
+    assert_close(C.cpu().numpy().reshape(N, B, 64), np.swapaxes(cref, 0, 1), "fused_fft_cgemm")
+    # fused CGEMM + iFFT from compact A[k][M]
+    A = _dev(cuda, np.swapaxes(spec, 0, 1).astype(np.complex64).reshape(K, M))
+    out = torch.empty((N, B, DY), dtype=torch.complex64, device=cuda)
+    t.fused_cgemm_ifft(M, N, K, A, wd, None, out, DY=DY)
+    yref = oracle_np.spectral_conv_1d(x, w, scale=False)
+    assert_close(np.swapaxes(out.cpu().numpy(), 0, 1), yref, "fused_cgemm_ifft")
+    # fully fused, kernel-table signature
+    out2 = torch.empty((N, B, DY), dtype=torch.complex64, device=cuda)
+    t.fused_fft_cgemm_ifft(M, N, K, xd, wd, None, out2, DY=DY)
+    assert_close(np.swapaxes(out2.cpu().numpy(), 0, 1), yref, "fused_fft_cgemm_ifft")

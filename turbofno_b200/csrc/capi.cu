@@ -1,0 +1,617 @@
+// C ABI of turbofno_b200: handle / plan / exec and the stage-level entry points.
+// Declarations and the reference interfaces they replace: include/turbofno_b200.h.
+#include <cublas_v2.h>
+#include <cufft.h>
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+#include "launch.cuh"
+
+using namespace tfno;
+
+struct tfno_handle_s {
+    DeviceInfo dev;
+};
+
+struct HostStaging {
+    bool ready = false;
+    long long chunk_rows = 0;           // batch items per pipeline chunk
+    float2* dx[2] = {nullptr, nullptr};
+    float2* dy[2] = {nullptr, nullptr};
+    void* dws[2] = {nullptr, nullptr};
+    float2* dw = nullptr;
+    cudaStream_t stream[2] = {nullptr, nullptr};
+    tfno_plan_s* chunk_plan = nullptr;  // plan for chunk_rows batch items
+    tfno_plan_s* tail_plan = nullptr;   // plan for the last, shorter chunk (if any)
+    long long tail_rows = 0;
+};
+
+struct tfno_plan_s {
+    tfno_handle_s* h = nullptr;
+    tfno_problem p{};
+    long long B = 0;                    // 1D: bs*dimX rows; 2D: bs images per channel
+    size_t ws_bytes = 0;
+    bool default_layout = true;
+    // variant E
+    cufftHandle fft_fwd = 0, fft_inv = 0;
+    bool have_fft = false;
+    cublasHandle_t blas = nullptr;
+    HostStaging host;
+};
+
+namespace {
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+        if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline float2 f2(float a, float b) { return make_float2(a, b); }
+inline float2 cscale(float2 a, float s) { return make_float2(a.x * s, a.y * s); }
+inline size_t align_up(size_t v) { return (v + 255) & ~(size_t)255; }
+
+long long image_elems(const tfno_problem& p) { return (long long)p.DX * p.DY; }
+
+// workspace carving: A/S (spectrum of x), C (spectrum of y), T1/T2 (X-transformed 64-row images),
+// F (full-size transform buffer of the library path)
+struct Workspace {
+    size_t offA = 0, offC = 0, offT1 = 0, offT2 = 0, offF = 0, total = 0;
+};
+
+Workspace carve(const tfno_plan_s& pl) {
+    const tfno_problem& p = pl.p;
+    Workspace w;
+    const long long per_row = (p.rank == 1) ? kModes : (long long)kModes * kModes;
+    const size_t szA = align_up(sizeof(float2) * (size_t)(p.K * pl.B * per_row));
+    const size_t szC = align_up(sizeof(float2) * (size_t)(p.N * pl.B * per_row));
+    size_t off = 0;
+    auto take = [&](size_t& slot, size_t sz) { slot = off; off += sz; };
+    const int v = p.variant;
+    if (p.rank == 1) {
+        if (v == TFNO_VARIANT_A || v == TFNO_VARIANT_C || v == TFNO_VARIANT_E) take(w.offA, szA);
+        if (v == TFNO_VARIANT_A || v == TFNO_VARIANT_B || v == TFNO_VARIANT_E) take(w.offC, szC);
+        if (v == TFNO_VARIANT_E) take(w.offF, align_up(sizeof(float2) * (size_t)(p.K * pl.B * p.DY)));
+    } else {
+        const size_t szT1 = align_up(sizeof(float2) * (size_t)(p.K * pl.B * kModes * p.DY));
+        const size_t szT2 = align_up(sizeof(float2) * (size_t)(p.N * pl.B * kModes * p.DY));
+        if (v == TFNO_VARIANT_A || v == TFNO_VARIANT_C || v == TFNO_VARIANT_D || v == TFNO_VARIANT_E) take(w.offA, szA);
+        if (v == TFNO_VARIANT_A || v == TFNO_VARIANT_B || v == TFNO_VARIANT_D || v == TFNO_VARIANT_E) take(w.offC, szC);
+        if (v == TFNO_VARIANT_A || v == TFNO_VARIANT_B || v == TFNO_VARIANT_C) { take(w.offT1, szT1); take(w.offT2, szT2); }
+        if (v == TFNO_VARIANT_E) take(w.offF, align_up(sizeof(float2) * (size_t)(p.K * pl.B * image_elems(p))));
+    }
+    w.total = off;
+    return w;
+}
+
+int validate(const tfno_problem& p) {
+    if (p.rank != 1 && p.rank != 2) return TFNO_ERR_INVALID_ARG;
+    if (p.bs <= 0 || p.K <= 0 || p.N <= 0) return TFNO_ERR_INVALID_ARG;
+    if (p.rank == 1 && p.dimX <= 0) return TFNO_ERR_INVALID_ARG;
+    if (p.variant < TFNO_VARIANT_A || p.variant > TFNO_VARIANT_E) return TFNO_ERR_INVALID_ARG;
+    if (p.modes != kModes) return TFNO_ERR_UNSUPPORTED;
+    if (!supported_len(p.DY)) return TFNO_ERR_UNSUPPORTED;
+    if (p.rank == 2 && !supported_len(p.DX)) return TFNO_ERR_UNSUPPORTED;
+    if (p.K % kSlabK != 0 || p.N % 64 != 0) return TFNO_ERR_UNSUPPORTED;
+    if (p.rank == 2 && p.variant == TFNO_VARIANT_D && (p.DX > 256 || p.DY > 256)) return TFNO_ERR_UNSUPPORTED;
+    return TFNO_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* tfno_status_string(int status) {
+    switch (status) {
+        case TFNO_OK: return "ok";
+        case TFNO_ERR_INVALID_ARG: return "invalid argument (null or misaligned pointer, non-positive size)";
+        case TFNO_ERR_UNSUPPORTED: return "unsupported size (need DY,DX in {128,256,512,1024}, K%8==0, N%64==0, modes==64)";
+        case TFNO_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
+        case TFNO_ERR_ALLOC: return "allocation failed";
+        case TFNO_ERR_LIBRARY: return "cuFFT or cuBLAS call failed";
+        case TFNO_ERR_WORKSPACE: return "workspace pointer missing";
+    }
+    return "unknown status";
+}
+
+int tfno_problem_init(tfno_problem* p, int rank) {
+    if (!p || (rank != 1 && rank != 2)) return TFNO_ERR_INVALID_ARG;
+    std::memset(p, 0, sizeof(*p));
+    p->rank = rank;
+    p->bs = 1;
+    p->dimX = 1;
+    p->DX = rank == 2 ? 256 : 1;
+    p->DY = 256;
+    p->K = 64;
+    p->N = 64;
+    p->modes = kModes;
+    p->variant = TFNO_VARIANT_D;
+    p->alpha_re = 1.f;
+    p->scale_inverse = 1;
+    return TFNO_OK;
+}
+
+int tfno_create(tfno_handle** out, int device) {
+    if (!out) return TFNO_ERR_INVALID_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) { cudaGetLastError(); return TFNO_ERR_CUDA; }
+    if (device < 0 || device >= count) return TFNO_ERR_INVALID_ARG;
+    tfno_handle_s* h = new (std::nothrow) tfno_handle_s();
+    if (!h) return TFNO_ERR_ALLOC;
+    h->dev.device = device;
+    if (cudaDeviceGetAttribute(&h->dev.sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&h->dev.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess) {
+        cudaGetLastError();
+        delete h;
+        return TFNO_ERR_CUDA;
+    }
+    *out = h;
+    return TFNO_OK;
+}
+
+int tfno_destroy(tfno_handle* h) {
+    delete h;
+    return TFNO_OK;
+}
+
+int tfno_sm_count(const tfno_handle* h, int* out) {
+    if (!h || !out) return TFNO_ERR_INVALID_ARG;
+    *out = h->dev.sms;
+    return TFNO_OK;
+}
+
+int tfno_plan_destroy(tfno_plan* plan) {
+    if (!plan) return TFNO_OK;
+    DeviceGuard guard(plan->h->dev.device);
+    if (plan->have_fft) { cufftDestroy(plan->fft_fwd); cufftDestroy(plan->fft_inv); }
+    if (plan->blas) cublasDestroy(plan->blas);
+    HostStaging& hs = plan->host;
+    for (int i = 0; i < 2; ++i) {
+        if (hs.dx[i]) cudaFree(hs.dx[i]);
+        if (hs.dy[i]) cudaFree(hs.dy[i]);
+        if (hs.dws[i]) cudaFree(hs.dws[i]);
+        if (hs.stream[i]) cudaStreamDestroy(hs.stream[i]);
+    }
+    if (hs.dw) cudaFree(hs.dw);
+    if (hs.chunk_plan) tfno_plan_destroy(hs.chunk_plan);
+    if (hs.tail_plan) tfno_plan_destroy(hs.tail_plan);
+    delete plan;
+    return TFNO_OK;
+}
+
+int tfno_plan_create(tfno_handle* h, const tfno_problem* problem, tfno_plan** out) {
+    if (!h || !problem || !out) return TFNO_ERR_INVALID_ARG;
+    *out = nullptr;
+    int rc = validate(*problem);
+    if (rc != TFNO_OK) return rc;
+    tfno_plan_s* pl = new (std::nothrow) tfno_plan_s();
+    if (!pl) return TFNO_ERR_ALLOC;
+    pl->h = h;
+    pl->p = *problem;
+    tfno_problem& p = pl->p;
+    pl->B = (p.rank == 1) ? p.bs * p.dimX : p.bs;
+    const long long unit = (p.rank == 1) ? p.DY : image_elems(p);
+    pl->default_layout = (p.x_stride_b == 0 || (p.x_stride_b == unit && p.x_stride_k == pl->B * unit)) &&
+                         (p.y_stride_b == 0 || (p.y_stride_b == unit && p.y_stride_n == pl->B * unit)) &&
+                         (p.w_stride_k == 0 || (p.w_stride_k == 1 && p.w_stride_n == p.K));
+    if (p.x_stride_b == 0) { p.x_stride_b = unit; p.x_stride_k = pl->B * unit; }
+    if (p.y_stride_b == 0) { p.y_stride_b = unit; p.y_stride_n = pl->B * unit; }
+    if (p.w_stride_k == 0) { p.w_stride_k = 1; p.w_stride_n = p.K; }
+    if ((p.x_stride_b | p.x_stride_k | p.y_stride_b | p.y_stride_n) & 1) {   // 16-byte alignment of rows
+        delete pl;
+        return TFNO_ERR_INVALID_ARG;
+    }
+    pl->ws_bytes = carve(*pl).total;
+
+    if (p.variant == TFNO_VARIANT_E) {
+        if (!pl->default_layout) { delete pl; return TFNO_ERR_UNSUPPORTED; }
+        DeviceGuard guard(h->dev.device);
+        if (!guard.ok) { delete pl; return TFNO_ERR_CUDA; }
+        // handles per plan, as the reference creates them per configuration
+        // (fusion_variants/1D_E_baseline/fused.cu:171-179); unlike the reference they are destroyed.
+        if (cublasCreate(&pl->blas) != CUBLAS_STATUS_SUCCESS) { pl->blas = nullptr; tfno_plan_destroy(pl); return TFNO_ERR_LIBRARY; }
+        cufftResult r1, r2;
+        if (p.rank == 1) {
+            r1 = cufftPlan1d(&pl->fft_fwd, p.DY, CUFFT_C2C, (int)(p.K * pl->B));
+            r2 = (r1 == CUFFT_SUCCESS) ? cufftPlan1d(&pl->fft_inv, p.DY, CUFFT_C2C, (int)(p.N * pl->B)) : r1;
+        } else {
+            int n[2] = {p.DX, p.DY};
+            r1 = cufftPlanMany(&pl->fft_fwd, 2, n, nullptr, 1, p.DX * p.DY, nullptr, 1, p.DX * p.DY, CUFFT_C2C, (int)(p.K * pl->B));
+            r2 = (r1 == CUFFT_SUCCESS)
+                     ? cufftPlanMany(&pl->fft_inv, 2, n, nullptr, 1, p.DX * p.DY, nullptr, 1, p.DX * p.DY, CUFFT_C2C, (int)(p.N * pl->B))
+                     : r1;
+        }
+        if (r1 != CUFFT_SUCCESS || r2 != CUFFT_SUCCESS) {
+            if (r1 == CUFFT_SUCCESS) cufftDestroy(pl->fft_fwd);
+            tfno_plan_destroy(pl);
+            return TFNO_ERR_LIBRARY;
+        }
+        pl->have_fft = true;
+    }
+    *out = pl;
+    return TFNO_OK;
+}
+
+size_t tfno_workspace_bytes(const tfno_plan* plan) { return plan ? plan->ws_bytes : 0; }
+
+int tfno_exec(const tfno_plan* plan, const void* x, const void* w, void* y, void* workspace, void* stream) {
+    if (!plan || !x || !w || !y) return TFNO_ERR_INVALID_ARG;
+    if (!aligned16(x) || !aligned16(y) || !aligned16(w) || !aligned16(workspace)) return TFNO_ERR_INVALID_ARG;
+    if (plan->ws_bytes > 0 && !workspace) return TFNO_ERR_WORKSPACE;
+    const tfno_problem& p = plan->p;
+    const DeviceInfo& dev = plan->h->dev;
+    DeviceGuard guard(dev.device);
+    if (!guard.ok) return TFNO_ERR_CUDA;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const Workspace ws = carve(*plan);
+    char* wsb = static_cast<char*>(workspace);
+    float2* A = reinterpret_cast<float2*>(wsb + ws.offA);
+    float2* C = reinterpret_cast<float2*>(wsb + ws.offC);
+    float2* T1 = reinterpret_cast<float2*>(wsb + ws.offT1);
+    float2* T2 = reinterpret_cast<float2*>(wsb + ws.offT2);
+    float2* F = reinterpret_cast<float2*>(wsb + ws.offF);
+
+    const float2 alpha = f2(p.alpha_re, p.alpha_im), beta = f2(p.beta_re, p.beta_im);
+    const int conj = p.second_transform_forward ? 0 : 1;
+    const float scale = p.scale_inverse ? 1.0f / (p.rank == 1 ? (float)p.DY : (float)p.DX * (float)p.DY) : 1.0f;
+    const long long B = plan->B;
+    const float2* xin = static_cast<const float2*>(x);
+    const float2* win = static_cast<const float2*>(w);
+    float2* yout = static_cast<float2*>(y);
+    int rc = TFNO_OK;
+
+    // operand descriptions reused below
+    TileParams t{};
+    t.K = p.K; t.N = p.N;
+    t.w = win; t.w_stride_k = p.w_stride_k; t.w_stride_n = p.w_stride_n;
+    t.alpha = alpha; t.beta = beta; t.conj_inverse = conj;
+
+    if (p.rank == 1) {
+        const long long M = B * kModes;
+        (void)M;
+        RowsParams fr{};   // x -> A
+        fr.nsig = p.K * B; fr.per_k = B; fr.in = xin; fr.out = A; fr.stride_row = p.x_stride_b; fr.stride_k = p.x_stride_k;
+        RowsParams ir{};   // C -> y
+        ir.nsig = p.N * B; ir.per_k = B; ir.in = C; ir.out = yout; ir.stride_row = p.y_stride_b; ir.stride_k = p.y_stride_n;
+        ir.gain = f2(scale, 0.f); ir.conj_inverse = conj;
+        t.rows = B;
+        switch (p.variant) {
+            case TFNO_VARIANT_A:
+                rc = launch_fft_rows(dev, p.DY, fr, st);
+                if (rc) return rc;
+                t.x = A; t.y = C;
+                rc = launch_tile<false, false>(dev, p.DY, t, st);
+                if (rc) return rc;
+                return launch_ifft_rows(dev, p.DY, ir, st);
+            case TFNO_VARIANT_B:
+                t.x = xin; t.x_stride_row = p.x_stride_b; t.x_stride_k = p.x_stride_k; t.y = C;
+                rc = launch_tile<true, false>(dev, p.DY, t, st);
+                if (rc) return rc;
+                return launch_ifft_rows(dev, p.DY, ir, st);
+            case TFNO_VARIANT_C:
+                rc = launch_fft_rows(dev, p.DY, fr, st);
+                if (rc) return rc;
+                t.x = A; t.y = yout; t.y_stride_row = p.y_stride_b; t.y_stride_n = p.y_stride_n;
+                t.inv_gain = cscale(alpha, scale);
+                return launch_tile<false, true>(dev, p.DY, t, st);
+            case TFNO_VARIANT_D:
+                t.x = xin; t.x_stride_row = p.x_stride_b; t.x_stride_k = p.x_stride_k;
+                t.y = yout; t.y_stride_row = p.y_stride_b; t.y_stride_n = p.y_stride_n;
+                t.inv_gain = cscale(alpha, scale);
+                return launch_tile<true, true>(dev, p.DY, t, st);
+            default: break;
+        }
+    } else {
+        const long long rows = B * kModes;       // 64-mode row tiles: one per (batch, kx)
+        ImageParams fi{};  // x -> A
+        fi.nimg = p.K * B; fi.per_k = B; fi.in = xin; fi.out = A; fi.stride_b = p.x_stride_b; fi.stride_k = p.x_stride_k;
+        ImageParams ii{};  // C -> y
+        ii.nimg = p.N * B; ii.per_k = B; ii.in = C; ii.out = yout; ii.stride_b = p.y_stride_b; ii.stride_k = p.y_stride_n;
+        ii.gain = f2(scale, 0.f); ii.conj_inverse = conj;
+        ColsParams fc{};   // x -> T1  [K*B][64][DY]
+        fc.nimg = p.K * B; fc.per_k = B; fc.DY = p.DY; fc.in = xin; fc.out = T1; fc.stride_b = p.x_stride_b; fc.stride_k = p.x_stride_k;
+        ColsParams ic{};   // T2 -> y
+        ic.nimg = p.N * B; ic.per_k = B; ic.DY = p.DY; ic.in = T2; ic.out = yout; ic.stride_b = p.y_stride_b; ic.stride_k = p.y_stride_n;
+        ic.gain = f2(scale, 0.f); ic.conj_inverse = conj;
+        RowsParams fr{};   // T1 -> A   (compact both sides)
+        fr.nsig = p.K * rows; fr.per_k = p.K * rows; fr.in = T1; fr.out = A; fr.stride_row = p.DY; fr.stride_k = 0;
+        RowsParams ir{};   // C -> T2
+        ir.nsig = p.N * rows; ir.per_k = p.N * rows; ir.in = C; ir.out = T2; ir.stride_row = p.DY; ir.stride_k = 0;
+        ir.gain = f2(1.f, 0.f); ir.conj_inverse = conj;
+        t.rows = rows;
+        switch (p.variant) {
+            case TFNO_VARIANT_D:
+                rc = launch_fft2d(dev, p.DX, p.DY, fi, false, st);
+                if (rc) return rc;
+                t.x = A; t.y = C;
+                rc = launch_tile<false, false>(dev, p.DY, t, st);
+                if (rc) return rc;
+                return launch_fft2d(dev, p.DX, p.DY, ii, true, st);
+            case TFNO_VARIANT_A:
+                rc = launch_fft_cols(dev, p.DX, fc, st);
+                if (rc) return rc;
+                rc = launch_fft_rows(dev, p.DY, fr, st);
+                if (rc) return rc;
+                t.x = A; t.y = C;
+                rc = launch_tile<false, false>(dev, p.DY, t, st);
+                if (rc) return rc;
+                rc = launch_ifft_rows(dev, p.DY, ir, st);
+                if (rc) return rc;
+                return launch_ifft_cols(dev, p.DX, ic, st);
+            case TFNO_VARIANT_B:
+                rc = launch_fft_cols(dev, p.DX, fc, st);
+                if (rc) return rc;
+                t.x = T1; t.x_stride_row = p.DY; t.x_stride_k = rows * p.DY; t.y = C;
+                rc = launch_tile<true, false>(dev, p.DY, t, st);
+                if (rc) return rc;
+                rc = launch_ifft_rows(dev, p.DY, ir, st);
+                if (rc) return rc;
+                return launch_ifft_cols(dev, p.DX, ic, st);
+            case TFNO_VARIANT_C:
+                rc = launch_fft_cols(dev, p.DX, fc, st);
+                if (rc) return rc;
+                rc = launch_fft_rows(dev, p.DY, fr, st);
+                if (rc) return rc;
+                t.x = A; t.y = T2; t.y_stride_row = p.DY; t.y_stride_n = rows * p.DY;
+                t.inv_gain = alpha;
+                rc = launch_tile<false, true>(dev, p.DY, t, st);
+                if (rc) return rc;
+                return launch_ifft_cols(dev, p.DX, ic, st);
+            default: break;
+        }
+    }
+
+    // ---- variant E: cuFFT -> truncate -> cuBLAS CGEMM -> zero-pad -> cuFFT ----------------------
+    // call sequence of fusion_variants/1D_E_baseline/fused.cu:200-216 and
+    // fusion_variants/2D_E_baseline/fused_trunc_2D.cu:238-253, stream-ordered, without the host
+    // synchronisation after every step.  The 1/len scale rides on alpha (beta must then be 0 for
+    // FNO semantics; with scale_inverse = 0 any beta behaves as in the reference).
+    if (cufftSetStream(plan->fft_fwd, st) != CUFFT_SUCCESS || cufftSetStream(plan->fft_inv, st) != CUFFT_SUCCESS ||
+        cublasSetStream(plan->blas, st) != CUBLAS_STATUS_SUCCESS)
+        return TFNO_ERR_LIBRARY;
+    if (cufftExecC2C(plan->fft_fwd, (cufftComplex*)xin, (cufftComplex*)F, CUFFT_FORWARD) != CUFFT_SUCCESS)
+        return TFNO_ERR_LIBRARY;
+    const int copy_blocks = dev.sms * 8;
+    const long long per_row = (p.rank == 1) ? kModes : (long long)kModes * kModes;
+    const long long Mlib = B * per_row;
+    if (p.rank == 1)
+        truncate_rows_kernel<<<copy_blocks, 256, 0, st>>>((const float4*)F, (float4*)A, p.K * B, p.DY);
+    else
+        truncate_corner_kernel<<<copy_blocks, 256, 0, st>>>((const float4*)F, (float4*)A, p.K * B, p.DX, p.DY);
+    if ((rc = launch_status())) return rc;
+    const float2 a2 = cscale(alpha, scale);
+    if (cublasCgemm(plan->blas, CUBLAS_OP_N, CUBLAS_OP_N, (int)Mlib, p.N, p.K, (const cuComplex*)&a2, (const cuComplex*)A,
+                    (int)Mlib, (const cuComplex*)win, p.K, (const cuComplex*)&beta, (cuComplex*)C, (int)Mlib) !=
+        CUBLAS_STATUS_SUCCESS)
+        return TFNO_ERR_LIBRARY;
+    if (p.rank == 1)
+        zero_pad_rows_kernel<<<copy_blocks, 256, 0, st>>>((const float4*)C, (float4*)yout, p.N * B, p.DY);
+    else
+        zero_pad_corner_kernel<<<copy_blocks, 256, 0, st>>>((const float4*)C, (float4*)yout, p.N * B, p.DX, p.DY);
+    if ((rc = launch_status())) return rc;
+    if (cufftExecC2C(plan->fft_inv, (cufftComplex*)yout, (cufftComplex*)yout, conj ? CUFFT_INVERSE : CUFFT_FORWARD) !=
+        CUFFT_SUCCESS)
+        return TFNO_ERR_LIBRARY;
+    return TFNO_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host-buffer execution: batch chunks pipelined over two streams (copy-in, layer, copy-out each
+// stream-ordered; the two streams overlap one another's copies and kernels).
+// ------------------------------------------------------------------------------------------------
+static int host_staging_init(tfno_plan_s* plan) {
+    HostStaging& hs = plan->host;
+    if (hs.ready) return TFNO_OK;
+    const tfno_problem& p = plan->p;
+    const long long unit = (p.rank == 1) ? (long long)p.dimX * p.DY : image_elems(p);   // elements per batch item and channel
+    // aim at ~64 MiB of input per chunk, at least 1 batch item, at most the whole batch
+    long long chunk = (64LL << 20) / (long long)(sizeof(float2) * unit * p.K);
+    if (chunk < 1) chunk = 1;
+    if (chunk > p.bs) chunk = p.bs;
+    hs.chunk_rows = chunk;
+    hs.tail_rows = p.bs % chunk;
+    tfno_problem cp = p;
+    cp.bs = chunk;
+    cp.x_stride_b = cp.x_stride_k = cp.y_stride_b = cp.y_stride_n = 0;
+    int rc = tfno_plan_create(plan->h, &cp, &hs.chunk_plan);
+    if (rc) return rc;
+    if (hs.tail_rows) {
+        cp.bs = hs.tail_rows;
+        rc = tfno_plan_create(plan->h, &cp, &hs.tail_plan);
+        if (rc) return rc;
+    }
+    const size_t xin = sizeof(float2) * (size_t)(unit * p.K * chunk), yout = sizeof(float2) * (size_t)(unit * p.N * chunk);
+    const size_t wsz = hs.chunk_plan->ws_bytes;
+    for (int i = 0; i < 2; ++i) {
+        if (cudaMalloc(&hs.dx[i], xin) != cudaSuccess || cudaMalloc(&hs.dy[i], yout) != cudaSuccess ||
+            (wsz && cudaMalloc(&hs.dws[i], wsz) != cudaSuccess) ||
+            cudaStreamCreateWithFlags(&hs.stream[i], cudaStreamNonBlocking) != cudaSuccess) {
+            cudaGetLastError();
+            return TFNO_ERR_ALLOC;
+        }
+    }
+    if (cudaMalloc(&hs.dw, sizeof(float2) * (size_t)p.K * p.N) != cudaSuccess) { cudaGetLastError(); return TFNO_ERR_ALLOC; }
+    hs.ready = true;
+    return TFNO_OK;
+}
+
+int tfno_exec_host(tfno_plan* plan, const void* x_host, const void* w_host, void* y_host) {
+    if (!plan || !x_host || !w_host || !y_host) return TFNO_ERR_INVALID_ARG;
+    if (!plan->default_layout) return TFNO_ERR_UNSUPPORTED;
+    DeviceGuard guard(plan->h->dev.device);
+    if (!guard.ok) return TFNO_ERR_CUDA;
+    int rc = host_staging_init(plan);
+    if (rc) return rc;
+    HostStaging& hs = plan->host;
+    const tfno_problem& p = plan->p;
+    const long long unit = (p.rank == 1) ? (long long)p.dimX * p.DY : image_elems(p);
+    const size_t full_pitch = sizeof(float2) * (size_t)(unit * p.bs);   // bytes between channels on the host
+    if (cudaMemcpyAsync(hs.dw, w_host, sizeof(float2) * (size_t)p.K * p.N, cudaMemcpyHostToDevice, hs.stream[0]) != cudaSuccess ||
+        cudaStreamSynchronize(hs.stream[0]) != cudaSuccess) {
+        cudaGetLastError();
+        return TFNO_ERR_CUDA;
+    }
+    int slot = 0;
+    for (long long b0 = 0; b0 < p.bs; b0 += hs.chunk_rows, slot ^= 1) {
+        const long long nb = (p.bs - b0 < hs.chunk_rows) ? p.bs - b0 : hs.chunk_rows;
+        tfno_plan_s* cp = (nb == hs.chunk_rows) ? hs.chunk_plan : hs.tail_plan;
+        const size_t width = sizeof(float2) * (size_t)(unit * nb);
+        cudaStream_t st = hs.stream[slot];
+        // [K][bs][unit] on the host -> compact [K][nb][unit] on the device
+        if (cudaMemcpy2DAsync(hs.dx[slot], width, static_cast<const char*>(x_host) + sizeof(float2) * (size_t)(unit * b0),
+                              full_pitch, width, (size_t)p.K, cudaMemcpyHostToDevice, st) != cudaSuccess) {
+            cudaGetLastError();
+            return TFNO_ERR_CUDA;
+        }
+        rc = tfno_exec(cp, hs.dx[slot], hs.dw, hs.dy[slot], hs.dws[slot], st);
+        if (rc) return rc;
+        if (cudaMemcpy2DAsync(static_cast<char*>(y_host) + sizeof(float2) * (size_t)(unit * b0), full_pitch, hs.dy[slot], width,
+                              width, (size_t)p.N, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
+            cudaGetLastError();
+            return TFNO_ERR_CUDA;
+        }
+    }
+    if (cudaStreamSynchronize(hs.stream[0]) != cudaSuccess || cudaStreamSynchronize(hs.stream[1]) != cudaSuccess) {
+        cudaGetLastError();
+        return TFNO_ERR_CUDA;
+    }
+    return TFNO_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Stage-level entry points
+// ------------------------------------------------------------------------------------------------
+static int check_stage(tfno_handle* h, const void* a, const void* b, const void* c) {
+    if (!h || !a || !b || !c) return TFNO_ERR_INVALID_ARG;
+    if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return TFNO_ERR_INVALID_ARG;
+    return TFNO_OK;
+}
+
+static TileParams stage_tile(long long M, int N, int K, const void* in, const void* B, void* out, float ar, float ai,
+                             float br, float bi) {
+    TileParams t{};
+    t.rows = M / kModes; t.K = K; t.N = N;
+    t.x = static_cast<const float2*>(in);
+    t.w = static_cast<const float2*>(B); t.w_stride_k = 1; t.w_stride_n = K;
+    t.y = static_cast<float2*>(out);
+    t.alpha = f2(ar, ai); t.beta = f2(br, bi);
+    t.inv_gain = t.alpha; t.conj_inverse = 1;
+    return t;
+}
+
+int tfno_fused_fft_cgemm_ifft(tfno_handle* h, int log2_len, long long M, int N, int K, const void* in, const void* B,
+                              void* C, void* out, float ar, float ai, float br, float bi, void* stream) {
+    (void)C;
+    int rc = check_stage(h, in, B, out);
+    if (rc) return rc;
+    if (M <= 0 || M % kModes) return TFNO_ERR_INVALID_ARG;
+    if (log2_len < 7 || log2_len > 10) return TFNO_ERR_UNSUPPORTED;
+    DeviceGuard guard(h->dev.device);
+    const int len = 1 << log2_len;
+    TileParams t = stage_tile(M, N, K, in, B, out, ar, ai, br, bi);
+    t.x_stride_row = len; t.x_stride_k = t.rows * len;
+    t.y_stride_row = len; t.y_stride_n = t.rows * len;
+    return launch_tile<true, true>(h->dev, len, t, static_cast<cudaStream_t>(stream));
+}
+
+int tfno_fused_fft_cgemm(tfno_handle* h, int log2_len, long long M, int N, int K, const void* in, const void* B, void* C,
+                         float ar, float ai, float br, float bi, void* stream) {
+    int rc = check_stage(h, in, B, C);
+    if (rc) return rc;
+    if (M <= 0 || M % kModes) return TFNO_ERR_INVALID_ARG;
+    if (log2_len < 7 || log2_len > 10) return TFNO_ERR_UNSUPPORTED;
+    DeviceGuard guard(h->dev.device);
+    const int len = 1 << log2_len;
+    TileParams t = stage_tile(M, N, K, in, B, C, ar, ai, br, bi);
+    t.x_stride_row = len; t.x_stride_k = t.rows * len;
+    return launch_tile<true, false>(h->dev, len, t, static_cast<cudaStream_t>(stream));
+}
+
+int tfno_fused_cgemm_ifft(tfno_handle* h, int log2_len, long long M, int N, int K, const void* A, const void* B, void* C,
+                          void* out, float ar, float ai, float br, float bi, void* stream) {
+    (void)C;
+    int rc = check_stage(h, A, B, out);
+    if (rc) return rc;
+    if (M <= 0 || M % kModes) return TFNO_ERR_INVALID_ARG;
+    if (log2_len < 7 || log2_len > 10) return TFNO_ERR_UNSUPPORTED;
+    DeviceGuard guard(h->dev.device);
+    const int len = 1 << log2_len;
+    TileParams t = stage_tile(M, N, K, A, B, out, ar, ai, br, bi);
+    t.y_stride_row = len; t.y_stride_n = t.rows * len;
+    return launch_tile<false, true>(h->dev, len, t, static_cast<cudaStream_t>(stream));
+}
+
+int tfno_cgemm(tfno_handle* h, long long M, int N, int K, const void* A, const void* B, void* C, float ar, float ai,
+               float br, float bi, void* stream) {
+    int rc = check_stage(h, A, B, C);
+    if (rc) return rc;
+    if (M <= 0 || M % kModes) return TFNO_ERR_INVALID_ARG;
+    DeviceGuard guard(h->dev.device);
+    TileParams t = stage_tile(M, N, K, A, B, C, ar, ai, br, bi);
+    return launch_tile<false, false>(h->dev, 128, t, static_cast<cudaStream_t>(stream));
+}
+
+static RowsParams stage_rows(int len, const void* in, void* out, long long total, bool forward) {
+    RowsParams r{};
+    r.nsig = total; r.per_k = total > 0 ? total : 1;
+    r.in = static_cast<const float2*>(in); r.out = static_cast<float2*>(out);
+    r.stride_row = len; r.stride_k = 0;
+    r.gain = f2(1.f, 0.f); r.conj_inverse = 1;
+    (void)forward;
+    return r;
+}
+
+int tfno_fft_stride_DY(tfno_handle* h, int log2_len, const void* in, void* out, long long total, void* stream) {
+    int rc = check_stage(h, in, out, out);
+    if (rc) return rc;
+    if (total < 0) return TFNO_ERR_INVALID_ARG;
+    if (log2_len < 7 || log2_len > 10) return TFNO_ERR_UNSUPPORTED;
+    if (total == 0) return TFNO_OK;
+    DeviceGuard guard(h->dev.device);
+    return launch_fft_rows(h->dev, 1 << log2_len, stage_rows(1 << log2_len, in, out, total, true), static_cast<cudaStream_t>(stream));
+}
+
+int tfno_ifft_stride_DY(tfno_handle* h, int log2_len, const void* in, void* out, long long total, void* stream) {
+    int rc = check_stage(h, in, out, out);
+    if (rc) return rc;
+    if (total < 0) return TFNO_ERR_INVALID_ARG;
+    if (log2_len < 7 || log2_len > 10) return TFNO_ERR_UNSUPPORTED;
+    if (total == 0) return TFNO_OK;
+    DeviceGuard guard(h->dev.device);
+    return launch_ifft_rows(h->dev, 1 << log2_len, stage_rows(1 << log2_len, in, out, total, false), static_cast<cudaStream_t>(stream));
+}
+
+static int stage_cols(tfno_handle* h, int log2_len, const void* in, void* out, int DY, long long total_columns, bool fwd,
+                      void* stream) {
+    int rc = check_stage(h, in, out, out);
+    if (rc) return rc;
+    if (DY <= 0 || (DY & 1) || total_columns < 0 || total_columns % DY) return TFNO_ERR_INVALID_ARG;
+    if (log2_len < 7 || log2_len > 10) return TFNO_ERR_UNSUPPORTED;
+    if (total_columns == 0) return TFNO_OK;
+    DeviceGuard guard(h->dev.device);
+    const int len = 1 << log2_len;
+    ColsParams c{};
+    c.nimg = total_columns / DY; c.per_k = c.nimg; c.DY = DY;
+    c.in = static_cast<const float2*>(in); c.out = static_cast<float2*>(out);
+    c.stride_b = (long long)len * DY; c.stride_k = 0;
+    c.gain = f2(1.f, 0.f); c.conj_inverse = 1;
+    return fwd ? launch_fft_cols(h->dev, len, c, static_cast<cudaStream_t>(stream))
+               : launch_ifft_cols(h->dev, len, c, static_cast<cudaStream_t>(stream));
+}
+
+int tfno_fft_stride(tfno_handle* h, int log2_len, const void* in, void* out, int DY, long long total_columns, void* stream) {
+    return stage_cols(h, log2_len, in, out, DY, total_columns, true, stream);
+}
+int tfno_ifft_stride(tfno_handle* h, int log2_len, const void* in, void* out, int DY, long long total_columns, void* stream) {
+    return stage_cols(h, log2_len, in, out, DY, total_columns, false, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,176 @@
+// Host-side launch helpers shared by the C ABI: size dispatch (transform length -> lanes per
+// signal R, output channels -> accumulator blocks NB), shared-memory sizing and persistent grids.
+#pragma once
+#include <cuda_runtime.h>
+#include "../../include/turbofno_b200.h"
+#include "spectral_kernels.cuh"
+
+namespace tfno {
+
+struct DeviceInfo {
+    int device = 0;
+    int sms = 0;
+    int max_smem_optin = 0;
+};
+
+inline int log2_exact(long long v) {
+    int l = 0;
+    while ((1LL << l) < v) ++l;
+    return ((1LL << l) == v) ? l : -1;
+}
+inline bool supported_len(int len) { return len == 128 || len == 256 || len == 512 || len == 1024; }
+
+template <typename Kernel>
+inline int prepare_kernel(Kernel kernel, size_t smem, const DeviceInfo& dev, int* blocks_per_sm) {
+    if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            cudaGetLastError();
+            return TFNO_ERR_CUDA;
+        }
+    }
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kThreads, smem) != cudaSuccess || occ < 1) {
+        cudaGetLastError();
+        return TFNO_ERR_CUDA;
+    }
+    *blocks_per_sm = occ;
+    return TFNO_OK;
+}
+
+inline int launch_status() { return cudaGetLastError() == cudaSuccess ? TFNO_OK : TFNO_ERR_CUDA; }
+
+inline size_t tile_smem_bytes(int R, bool fwd, bool inv, int K, int N) {
+    size_t elems = (size_t)K * kModes + (inv ? (size_t)N * kModes : 0) + 2 * (size_t)kSlabK * (N + kWPad) +
+                   (fwd ? R * 64 : 0) + (inv ? R * 64 : 0);
+    return elems * sizeof(float2);
+}
+
+template <int R, bool FWD, bool INV, int NB>
+inline int launch_tile_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
+    auto kernel = spectral_tile_kernel<R, FWD, INV, NB>;
+    size_t smem = tile_smem_bytes(R, FWD, INV, p.K, p.N);
+    int occ = 0;
+    int rc = prepare_kernel(kernel, smem, dev, &occ);
+    if (rc != TFNO_OK) return rc;
+    long long grid = (long long)dev.sms * occ;
+    if (grid > p.rows) grid = p.rows;
+    kernel<<<(unsigned)grid, kThreads, smem, st>>>(p);
+    return launch_status();
+}
+
+template <bool FWD, bool INV, int NB>
+inline int launch_tile_r(const DeviceInfo& dev, int R, const TileParams& p, cudaStream_t st) {
+    switch (R) {
+        case 2: return launch_tile_inst<2, FWD, INV, NB>(dev, p, st);
+        case 4: return launch_tile_inst<4, FWD, INV, NB>(dev, p, st);
+        case 8: return launch_tile_inst<8, FWD, INV, NB>(dev, p, st);
+        case 16: return launch_tile_inst<16, FWD, INV, NB>(dev, p, st);
+    }
+    return TFNO_ERR_UNSUPPORTED;
+}
+
+// Row-tile kernel for any N that is a multiple of 64: output channels are processed in blocks of
+// at most 128 (one launch per block; N <= 128, the whole reference grid, is a single launch).
+template <bool FWD, bool INV>
+inline int launch_tile(const DeviceInfo& dev, int len, TileParams p, cudaStream_t st) {
+    if (p.rows <= 0) return TFNO_OK;
+    if (p.K < kSlabK || p.K % kSlabK != 0 || p.N < 64 || p.N % 64 != 0) return TFNO_ERR_UNSUPPORTED;
+    const int R = (FWD || INV) ? len / 64 : 2;      // the pure GEMM instance does not depend on R
+    if ((FWD || INV) && !supported_len(len)) return TFNO_ERR_UNSUPPORTED;
+    const int N = p.N;
+    const long long M = p.rows * kModes;
+    for (int n0 = 0; n0 < N; n0 += 128) {
+        TileParams q = p;
+        q.N = (N - n0 >= 128) ? 128 : 64;
+        q.w = p.w + (long long)n0 * p.w_stride_n;
+        q.y = p.y + (long long)n0 * (INV ? p.y_stride_n : M);
+        int rc = (q.N == 128) ? launch_tile_r<FWD, INV, 2>(dev, R, q, st) : launch_tile_r<FWD, INV, 1>(dev, R, q, st);
+        if (rc != TFNO_OK) return rc;
+    }
+    return TFNO_OK;
+}
+
+template <typename Params, typename Kernel>
+inline int launch_persistent(const DeviceInfo& dev, Kernel kernel, size_t smem, long long work_blocks,
+                             const Params& p, cudaStream_t st) {
+    if (work_blocks <= 0) return TFNO_OK;
+    int occ = 0;
+    int rc = prepare_kernel(kernel, smem, dev, &occ);
+    if (rc != TFNO_OK) return rc;
+    long long grid = (long long)dev.sms * occ;
+    if (grid > work_blocks) grid = work_blocks;
+    kernel<<<(unsigned)grid, kThreads, smem, st>>>(p);
+    return launch_status();
+}
+
+inline int launch_fft_rows(const DeviceInfo& dev, int len, const RowsParams& p, cudaStream_t st) {
+    const int R = len / 64;
+    const long long blocks = (p.nsig + kThreads / R - 1) / (kThreads / R);
+    switch (R) {
+        case 2: return launch_persistent(dev, fft_rows_trunc_kernel<2>, 0, blocks, p, st);
+        case 4: return launch_persistent(dev, fft_rows_trunc_kernel<4>, 0, blocks, p, st);
+        case 8: return launch_persistent(dev, fft_rows_trunc_kernel<8>, 0, blocks, p, st);
+        case 16: return launch_persistent(dev, fft_rows_trunc_kernel<16>, 0, blocks, p, st);
+    }
+    return TFNO_ERR_UNSUPPORTED;
+}
+inline int launch_ifft_rows(const DeviceInfo& dev, int len, const RowsParams& p, cudaStream_t st) {
+    const int R = len / 64;
+    const long long blocks = (p.nsig + kThreads / R - 1) / (kThreads / R);
+    switch (R) {
+        case 2: return launch_persistent(dev, ifft_rows_pad_kernel<2>, 0, blocks, p, st);
+        case 4: return launch_persistent(dev, ifft_rows_pad_kernel<4>, 0, blocks, p, st);
+        case 8: return launch_persistent(dev, ifft_rows_pad_kernel<8>, 0, blocks, p, st);
+        case 16: return launch_persistent(dev, ifft_rows_pad_kernel<16>, 0, blocks, p, st);
+    }
+    return TFNO_ERR_UNSUPPORTED;
+}
+inline int launch_fft_cols(const DeviceInfo& dev, int len, const ColsParams& p, cudaStream_t st) {
+    const int R = len / 64;
+    const long long blocks = (p.nimg * p.DY + kThreads / R - 1) / (kThreads / R);
+    switch (R) {
+        case 2: return launch_persistent(dev, fft_cols_trunc_kernel<2>, 0, blocks, p, st);
+        case 4: return launch_persistent(dev, fft_cols_trunc_kernel<4>, 0, blocks, p, st);
+        case 8: return launch_persistent(dev, fft_cols_trunc_kernel<8>, 0, blocks, p, st);
+        case 16: return launch_persistent(dev, fft_cols_trunc_kernel<16>, 0, blocks, p, st);
+    }
+    return TFNO_ERR_UNSUPPORTED;
+}
+inline int launch_ifft_cols(const DeviceInfo& dev, int len, const ColsParams& p, cudaStream_t st) {
+    const int R = len / 64;
+    const long long blocks = (p.nimg * p.DY + kThreads / R - 1) / (kThreads / R);
+    switch (R) {
+        case 2: return launch_persistent(dev, ifft_cols_pad_kernel<2>, 0, blocks, p, st);
+        case 4: return launch_persistent(dev, ifft_cols_pad_kernel<4>, 0, blocks, p, st);
+        case 8: return launch_persistent(dev, ifft_cols_pad_kernel<8>, 0, blocks, p, st);
+        case 16: return launch_persistent(dev, ifft_cols_pad_kernel<16>, 0, blocks, p, st);
+    }
+    return TFNO_ERR_UNSUPPORTED;
+}
+
+inline size_t image_smem_bytes(int DX, int DY) {
+    return ((size_t)DX * kModes + (DX / 64) * 64 + (DY / 64) * 64) * sizeof(float2);
+}
+template <int RX>
+inline int launch_fft2d_rx(const DeviceInfo& dev, int RY, const ImageParams& p, bool inverse, cudaStream_t st) {
+    const size_t smem = image_smem_bytes(64 * RX, 64 * RY);
+#define TFNO_IMG(RYV)                                                                              \
+    case RYV:                                                                                      \
+        return inverse ? launch_persistent(dev, ifft2d_pad_kernel<RX, RYV>, smem, p.nimg, p, st)   \
+                       : launch_persistent(dev, fft2d_trunc_kernel<RX, RYV>, smem, p.nimg, p, st);
+    switch (RY) { TFNO_IMG(2) TFNO_IMG(4) }
+#undef TFNO_IMG
+    return TFNO_ERR_UNSUPPORTED;
+}
+// whole-image kernels exist for DX, DY in {128, 256} (a 512-row intermediate would need 256 KB)
+inline int launch_fft2d(const DeviceInfo& dev, int DX, int DY, const ImageParams& p, bool inverse, cudaStream_t st) {
+    if (p.nimg <= 0) return TFNO_OK;
+    switch (DX / 64) {
+        case 2: return launch_fft2d_rx<2>(dev, DY / 64, p, inverse, st);
+        case 4: return launch_fft2d_rx<4>(dev, DY / 64, p, inverse, st);
+    }
+    return TFNO_ERR_UNSUPPORTED;
+}
+
+}  // namespace tfno
