@@ -1,5 +1,6 @@
 """ctypes loader for the C oracle (oracle/liboracle.so).  Test infrastructure only."""
 import ctypes
+import hashlib
 import os
 import subprocess
 
@@ -13,10 +14,16 @@ def build(force=False):
     so = os.path.join(_HERE, "liboracle.so")
     src = os.path.join(_HERE, "spectral_oracle.c")
     inc = os.path.join(_HERE, "spectral_oracle_impl.inc")
-    stale = (not os.path.exists(so)) or any(
-        os.path.exists(p) and os.path.getmtime(p) > os.path.getmtime(so) for p in (src, inc))
+    h = hashlib.sha256()
+    for p in (src, inc):
+        with open(p, "rb") as f:
+            h.update(f.read())
+    stamp = so + ".srchash"
+    stale = not (os.path.exists(so) and os.path.exists(stamp) and open(stamp).read().strip() == h.hexdigest())
     if force or stale:
         subprocess.check_call(["gcc", "-O3", "-march=x86-64-v3", "-fopenmp", "-shared", "-fPIC", src, "-o", so, "-lm"])
+        with open(stamp, "w") as f:
+            f.write(h.hexdigest())
     return so
 
 

@@ -3,6 +3,7 @@
 Run as `python -m turbofno_b200.build [--force] [--drivers]`.  Everything is built in-tree so
 that the shared library sits next to the package that loads it.
 """
+import hashlib
 import os
 import subprocess
 import sys
@@ -19,11 +20,29 @@ NVCC_FLAGS = [
 ]
 
 
-def _newer(target, sources):
-    if not os.path.exists(target):
+def _digest(sources, extra=""):
+    h = hashlib.sha256(extra.encode())
+    for s in sources:
+        if os.path.exists(s):
+            h.update(os.path.basename(s).encode())
+            with open(s, "rb") as f:
+                h.update(f.read())
+    return h.hexdigest()
+
+
+def _newer(target, sources, extra=""):
+    """True when `target` is missing or was built from different source contents.  Contents, not
+    timestamps: a copied tree does not keep the order of modification times."""
+    stamp = target + ".srchash"
+    if not os.path.exists(target) or not os.path.exists(stamp):
         return True
-    t = os.path.getmtime(target)
-    return any(os.path.getmtime(s) > t for s in sources if os.path.exists(s))
+    with open(stamp) as f:
+        return f.read().strip() != _digest(sources, extra)
+
+
+def _stamp(target, sources, extra=""):
+    with open(target + ".srchash", "w") as f:
+        f.write(_digest(sources, extra))
 
 
 def _lib_sources():
@@ -41,6 +60,7 @@ def build_library(force=False, verbose=False):
     if verbose:
         cmd += ["-Xptxas", "-v"]
     subprocess.check_call(cmd)
+    _stamp(LIB, srcs)
     return LIB
 
 
@@ -58,7 +78,8 @@ def build_drivers(force=False):
     for rank, v in VARIANTS:
         exe = os.path.join(BIN, "TurboFNO_%dD_%s" % (rank, v))
         cfg = os.path.join(PKG, "drivers", "benchmark_config", "problem_size_%dd.txt" % rank)
-        if force or _newer(exe, [src, LIB] + hdrs):
+        deps = [src, os.path.join(PKG, "drivers", "driver_config.h")] + hdrs
+        if force or _newer(exe, deps, extra=cfg):
             subprocess.check_call([
                 "g++", "-std=c++17", "-O2", "-I" + os.path.join(ROOT, "include"), "-I/usr/local/cuda/include",
                 "-DTFNO_RANK=%d" % rank, "-DTFNO_VARIANT=TFNO_VARIANT_%s" % v, '-DTFNO_TAG="%dD_%s"' % (rank, v),
@@ -66,6 +87,7 @@ def build_drivers(force=False):
                 "-L" + PKG, "-lturbofno_b200", "-L/usr/local/cuda/lib64", "-lcudart",
                 "-Wl,-rpath," + PKG, "-Wl,-rpath,/usr/local/cuda/lib64",
             ])
+            _stamp(exe, deps, extra=cfg)
         outs.append(exe)
     return outs
 
