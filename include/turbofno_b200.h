@@ -86,6 +86,10 @@ int tfno_problem_init(tfno_problem* p, int rank);
 /* Replaces the implicit device-0 context of every reference driver (no cudaSetDevice anywhere). */
 int tfno_create(tfno_handle** out, int device);
 int tfno_destroy(tfno_handle* h);
+/* Device-side status word of the handle: 0, or the code of the first bounded wait that ran out
+ * inside a kernel (the kernel then stops early and its output is incomplete).  Synchronises the
+ * device.  The reference has no counterpart: its kernels contain no waits. */
+int tfno_device_status(tfno_handle* h, int* out);
 /* number of SMs of the handle's device (148 on B200); grids are sized from it */
 int tfno_sm_count(const tfno_handle* h, int* out);
 

@@ -47,6 +47,7 @@ SYMBOLS = {
     "tfno_create": (_i, [ctypes.POINTER(_vp), _i]),
     "tfno_destroy": (_i, [_vp]),
     "tfno_sm_count": (_i, [_vp, ctypes.POINTER(_i)]),
+    "tfno_device_status": (_i, [_vp, ctypes.POINTER(_i)]),
     "tfno_plan_create": (_i, [_vp, ctypes.POINTER(Problem), ctypes.POINTER(_vp)]),
     "tfno_plan_destroy": (_i, [_vp]),
     "tfno_workspace_bytes": (ctypes.c_size_t, [_vp]),

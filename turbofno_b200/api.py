@@ -55,6 +55,13 @@ class Handle:
         check(self.lib.tfno_sm_count(self._h, ctypes.byref(n)), "tfno_sm_count")
         return n.value
 
+    @property
+    def device_status(self):
+        """0, or the code of a kernel-side wait that ran out (synchronises the device)."""
+        n = ctypes.c_int()
+        check(self.lib.tfno_device_status(self._h, ctypes.byref(n)), "tfno_device_status")
+        return n.value
+
     def close(self):
         if self._h:
             self.lib.tfno_destroy(self._h)

@@ -153,12 +153,38 @@ int tfno_create(tfno_handle** out, int device) {
         delete h;
         return TFNO_ERR_CUDA;
     }
+    {
+        DeviceGuard guard(device);
+        if (!guard.ok || cudaMalloc(&h->dev.status, sizeof(int)) != cudaSuccess ||
+            cudaMemset(h->dev.status, 0, sizeof(int)) != cudaSuccess) {
+            cudaGetLastError();
+            delete h;
+            return TFNO_ERR_ALLOC;
+        }
+    }
+    const char* no_tc = std::getenv("TFNO_DISABLE_TENSOR_CORES");
+    h->dev.use_tensor_cores = !(no_tc && no_tc[0] == '1');
     *out = h;
     return TFNO_OK;
 }
 
 int tfno_destroy(tfno_handle* h) {
+    if (!h) return TFNO_OK;
+    if (h->dev.status) {
+        DeviceGuard guard(h->dev.device);
+        cudaFree(h->dev.status);
+    }
     delete h;
+    return TFNO_OK;
+}
+
+int tfno_device_status(tfno_handle* h, int* out) {
+    if (!h || !out) return TFNO_ERR_INVALID_ARG;
+    DeviceGuard guard(h->dev.device);
+    if (!guard.ok || cudaMemcpy(out, h->dev.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return TFNO_ERR_CUDA;
+    }
     return TFNO_OK;
 }
 

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include "../../include/turbofno_b200.h"
 #include "spectral_kernels.cuh"
+#include "spectral_tc.cuh"
 
 namespace tfno {
 
@@ -11,6 +12,8 @@ struct DeviceInfo {
     int device = 0;
     int sms = 0;
     int max_smem_optin = 0;
+    bool use_tensor_cores = true;   // tcgen05 fused kernel where its shape limits allow
+    int* status = nullptr;          // device word written by kernels whose bounded waits ran out
 };
 
 inline int log2_exact(long long v) {
@@ -70,6 +73,36 @@ inline int launch_tile_r(const DeviceInfo& dev, int R, const TileParams& p, cuda
     return TFNO_ERR_UNSUPPORTED;
 }
 
+// Tensor-core fused kernel: N = 64, K a multiple of the chunk size (64/R channels) up to 64,
+// transform length 128 or 256.
+inline bool tc_eligible(const DeviceInfo& dev, int len, const TileParams& p) {
+    if (!dev.use_tensor_cores || !dev.status) return false;
+    if (p.N != 64 || (len != 128 && len != 256)) return false;
+    const int CH = 64 / (len / 64);
+    return p.K >= CH && p.K <= 64 && p.K % CH == 0;
+}
+
+template <int R>
+inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
+    auto kernel = tc::spectral_tc_kernel<R>;
+    const size_t smem = tc::tc_smem_bytes<R>(p.K);
+    if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return TFNO_ERR_CUDA;
+    }
+    tc::TcParams q{};
+    q.rows = p.rows; q.K = p.K;
+    q.x = p.x; q.x_stride_row = p.x_stride_row; q.x_stride_k = p.x_stride_k;
+    q.w = p.w; q.w_stride_k = p.w_stride_k; q.w_stride_n = p.w_stride_n;
+    q.y = p.y; q.y_stride_row = p.y_stride_row; q.y_stride_n = p.y_stride_n;
+    q.inv_gain = p.inv_gain; q.conj_inverse = p.conj_inverse; q.status = dev.status;
+    long long grid = dev.sms;
+    if (grid > p.rows) grid = p.rows;
+    kernel<<<(unsigned)grid, tc::kTcThreads, smem, st>>>(q);
+    return launch_status();
+}
+
 // Row-tile kernel for any N that is a multiple of 64: output channels are processed in blocks of
 // at most 128 (one launch per block; N <= 128, the whole reference grid, is a single launch).
 template <bool FWD, bool INV>
@@ -78,6 +111,9 @@ inline int launch_tile(const DeviceInfo& dev, int len, TileParams p, cudaStream_
     if (p.K < kSlabK || p.K % kSlabK != 0 || p.N < 64 || p.N % 64 != 0) return TFNO_ERR_UNSUPPORTED;
     const int R = (FWD || INV) ? len / 64 : 2;      // the pure GEMM instance does not depend on R
     if ((FWD || INV) && !supported_len(len)) return TFNO_ERR_UNSUPPORTED;
+    if constexpr (FWD && INV) {
+        if (tc_eligible(dev, len, p)) return len == 128 ? launch_tc_inst<2>(dev, p, st) : launch_tc_inst<4>(dev, p, st);
+    }
     const int N = p.N;
     const long long M = p.rows * kModes;
     for (int n0 = 0; n0 < N; n0 += 128) {
