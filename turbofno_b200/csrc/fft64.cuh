@@ -60,10 +60,28 @@ constexpr double cx_cos2pi(int num, int den) {
 constexpr double cx_sin2pi(int num, int den) { return cx_cos2pi(num - den / 4, den); }
 
 // ------------------------------------------------------------------------------------------
-// tiny complex helpers on float2
+// tiny complex helpers on float2.  On sm_100 a complex add / subtract / real-scaled accumulate
+// is ONE packed instruction (add.f32x2 / fma.rn.f32x2 on an aligned register pair); the host
+// build and older targets fall back to two scalar operations.
 // ------------------------------------------------------------------------------------------
-TFNO_HD float2 cadd(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
-TFNO_HD float2 csub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ >= 1000)
+#define TFNO_PACKED_F32X2 1
+#endif
+
+TFNO_HD float2 cadd(float2 a, float2 b) {
+#ifdef TFNO_PACKED_F32X2
+    return __fadd2_rn(a, b);
+#else
+    return make_float2(a.x + b.x, a.y + b.y);
+#endif
+}
+TFNO_HD float2 csub(float2 a, float2 b) {
+#ifdef TFNO_PACKED_F32X2
+    return __ffma2_rn(b, make_float2(-1.0f, -1.0f), a);
+#else
+    return make_float2(a.x - b.x, a.y - b.y);
+#endif
+}
 TFNO_HD float2 cmul(float2 a, float2 b) {
     return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
 }
@@ -71,8 +89,14 @@ TFNO_HD float2 cmul(float2 a, float2 b) {
 template <int S> TFNO_HD float2 mul_si(float2 a) {
     return S < 0 ? make_float2(a.y, -a.x) : make_float2(-a.y, a.x);
 }
-// e + s*t with a run-time real sign s
-TFNO_HD float2 cfma_s(float s, float2 t, float2 e) { return make_float2(fmaf(s, t.x, e.x), fmaf(s, t.y, e.y)); }
+// e + s*t for a real factor held twice in s2 = (s, s)
+TFNO_HD float2 cfma_s(float2 s2, float2 t, float2 e) {
+#ifdef TFNO_PACKED_F32X2
+    return __ffma2_rn(s2, t, e);
+#else
+    return make_float2(fmaf(s2.x, t.x, e.x), fmaf(s2.y, t.y, e.y));
+#endif
+}
 
 // register slot holding mode k after fft64()
 TFNO_HD constexpr int slot(int k) { return 8 * (k & 7) + (k >> 3); }
@@ -82,31 +106,53 @@ TFNO_HD constexpr int slot(int k) { return 8 * (k & 7) + (k >> 3); }
 // ------------------------------------------------------------------------------------------
 template <int S>
 TFNO_HD void dft4(float2& b0, float2& b1, float2& b2, float2& b3) {
-    float2 p0 = cadd(b0, b2), p1 = csub(b0, b2), p2 = cadd(b1, b3), p3 = mul_si<S>(csub(b1, b3));
+    const float2 p0 = cadd(b0, b2), p1 = csub(b0, b2), p2 = cadd(b1, b3);
+    // p3 = (S*i) * (b1 - b3), written component-wise so that the rotation costs no moves
+    const float2 p3 = S < 0 ? make_float2(b1.y - b3.y, b3.x - b1.x) : make_float2(b3.y - b1.y, b1.x - b3.x);
     b0 = cadd(p0, p2); b2 = csub(p0, p2); b1 = cadd(p1, p3); b3 = csub(p1, p3);
 }
 
+// Real sign s = +-1 of the odd-indexed inputs of fft8(), in the forms its last stage consumes.
+struct OddSign {
+    float s, ns;          // s, -s
+    float2 s2, ns2;       // (s, s), (-s, -s)
+    float2 sh2, nsh2;     // (s*h, s*h), (-s*h, -s*h), h = sqrt(1/2)
+};
+TFNO_HD OddSign make_odd_sign(float s) {
+    constexpr float h = 0.70710678118654752440f;
+    OddSign o;
+    o.s = s; o.ns = -s;
+    o.s2 = make_float2(s, s); o.ns2 = make_float2(-s, -s);
+    o.sh2 = make_float2(s * h, s * h); o.nsh2 = make_float2(-s * h, -s * h);
+    return o;
+}
+
 // Decimation-in-time radix-8.  Inputs a[j] at a0..a7, outputs X[k] returned in place (a_k = X[k]).
-// The odd-indexed inputs are taken as s*a[j] with a run-time s = +-1 (ns = -s): negating the
-// odd inputs rotates the output by four places, which the forward transform uses to make each
-// lane's "keep" half land in fixed registers.  With s = 1 known at compile time the multiplies
-// fold into plain adds.
+// The odd-indexed inputs are taken as s*a[j] with a run-time s = +-1: negating the odd inputs
+// rotates the output by four places, which the forward transform uses to make each lane's
+// "keep" half land in fixed registers.  The sign rides on the multiply-accumulates of the last
+// stage and costs nothing.
 template <int S>
 TFNO_HD void fft8(float2& a0, float2& a1, float2& a2, float2& a3, float2& a4, float2& a5, float2& a6,
-                  float2& a7, float s, float ns) {
-    constexpr float h = 0.70710678118654752440f;
+                  float2& a7, const OddSign& sg) {
     float2 e0 = a0, e1 = a2, e2 = a4, e3 = a6;
     float2 o0 = a1, o1 = a3, o2 = a5, o3 = a7;
     dft4<S>(e0, e1, e2, e3);
     dft4<S>(o0, o1, o2, o3);
-    // T[k] = O[k] * W8^k,  W8 = e^{S*2 pi i/8}
-    float2 t1 = make_float2((o1.x - S * o1.y) * h, (o1.y + S * o1.x) * h);
-    float2 t2 = mul_si<S>(o2);
-    float2 t3 = make_float2((-o3.x - S * o3.y) * h, (-o3.y + S * o3.x) * h);
-    a0 = cfma_s(s, o0, e0); a4 = cfma_s(ns, o0, e0);
-    a1 = cfma_s(s, t1, e1); a5 = cfma_s(ns, t1, e1);
-    a2 = cfma_s(s, t2, e2); a6 = cfma_s(ns, t2, e2);
-    a3 = cfma_s(s, t3, e3); a7 = cfma_s(ns, t3, e3);
+    // T[k] = O[k] * W8^k, W8 = e^{S*2 pi i/8}; the factor h of T1, T3 is folded into sh2 / nsh2,
+    // the rotation T2 = (S*i)*O2 into the operand order of four scalar multiply-accumulates
+    const float2 w1 = make_float2(o1.x - S * o1.y, o1.y + S * o1.x);
+    const float2 w3 = make_float2(-o3.x - S * o3.y, -o3.y + S * o3.x);
+    a0 = cfma_s(sg.s2, o0, e0);  a4 = cfma_s(sg.ns2, o0, e0);
+    a1 = cfma_s(sg.sh2, w1, e1); a5 = cfma_s(sg.nsh2, w1, e1);
+    a3 = cfma_s(sg.sh2, w3, e3); a7 = cfma_s(sg.nsh2, w3, e3);
+    if (S < 0) {
+        a2 = make_float2(fmaf(sg.s, o2.y, e2.x), fmaf(sg.ns, o2.x, e2.y));
+        a6 = make_float2(fmaf(sg.ns, o2.y, e2.x), fmaf(sg.s, o2.x, e2.y));
+    } else {
+        a2 = make_float2(fmaf(sg.ns, o2.y, e2.x), fmaf(sg.s, o2.x, e2.y));
+        a6 = make_float2(fmaf(sg.s, o2.y, e2.x), fmaf(sg.ns, o2.x, e2.y));
+    }
 }
 
 template <int S, int N2, int K1>
@@ -135,15 +181,15 @@ TFNO_HD void twiddle_row(float2* v) {   // v[8*K1 + n2] *= W64^{n2*K1}, n2 = 1..
 }
 
 // 64-point transform, in registers.  In: v[n] = sample n.  Out: mode k in v[slot(k)].
-// With s = -1 (ns = +1) the odd samples are negated, i.e. the output is rotated by 32:
+// With s = -1 the odd samples are negated, i.e. the output is rotated by 32:
 // v[slot(k)] then holds mode (k + 32) mod 64.
 template <int S>
-TFNO_HD void fft64(float2 (&v)[64], float s = 1.0f, float ns = -1.0f) {
+TFNO_HD void fft64(float2 (&v)[64], float s = 1.0f) {
+    const OddSign plus = make_odd_sign(1.0f), sg = make_odd_sign(s);
     // step 1: for every n2, radix-8 over n1 on v[8*n1 + n2]; result k1 stored at v[8*k1 + n2]
 #pragma unroll
     for (int n2 = 0; n2 < 8; ++n2)
-        fft8<S>(v[n2], v[8 + n2], v[16 + n2], v[24 + n2], v[32 + n2], v[40 + n2], v[48 + n2], v[56 + n2],
-                1.0f, -1.0f);
+        fft8<S>(v[n2], v[8 + n2], v[16 + n2], v[24 + n2], v[32 + n2], v[40 + n2], v[48 + n2], v[56 + n2], plus);
     // step 2: twiddles W64^{n2*k1}
     twiddle_row<S, 1>(v); twiddle_row<S, 2>(v); twiddle_row<S, 3>(v); twiddle_row<S, 4>(v);
     twiddle_row<S, 5>(v); twiddle_row<S, 6>(v); twiddle_row<S, 7>(v);
@@ -152,7 +198,7 @@ TFNO_HD void fft64(float2 (&v)[64], float s = 1.0f, float ns = -1.0f) {
 #pragma unroll
     for (int k1 = 0; k1 < 8; ++k1)
         fft8<S>(v[8 * k1], v[8 * k1 + 1], v[8 * k1 + 2], v[8 * k1 + 3], v[8 * k1 + 4], v[8 * k1 + 5],
-                v[8 * k1 + 6], v[8 * k1 + 7], s, ns);
+                v[8 * k1 + 6], v[8 * k1 + 7], sg);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -202,7 +248,7 @@ TFNO_HD void fill_inverse_table(float2* twI, int tid, int nthreads, float2 g, bo
 template <int R>
 TFNO_HD void forward_local(float2 (&v)[64], const float2* __restrict__ twF_r, int r) {
     const bool hi = (r & (R >> 1)) != 0;
-    fft64<-1>(v, hi ? -1.0f : 1.0f, hi ? 1.0f : -1.0f);
+    fft64<-1>(v, hi ? -1.0f : 1.0f);
 #pragma unroll
     for (int j = 0; j < 64; j += 2) {
         float4 t = *reinterpret_cast<const float4*>(twF_r + j);

@@ -2,6 +2,7 @@
 // signal R, output channels -> accumulator blocks NB), shared-memory sizing and persistent grids.
 #pragma once
 #include <cuda_runtime.h>
+#include <cstdio>
 #include "../../include/turbofno_b200.h"
 #include "spectral_kernels.cuh"
 #include "spectral_tc.cuh"
@@ -82,9 +83,9 @@ inline bool tc_eligible(const DeviceInfo& dev, int len, const TileParams& p) {
     return p.K >= CH && p.K <= 64 && p.K % CH == 0;
 }
 
-template <int R>
+template <int R, bool INVERSE>
 inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
-    auto kernel = tc::spectral_tc_kernel<R>;
+    auto kernel = tc::spectral_tc_kernel<R, INVERSE>;
     const size_t smem = tc::tc_smem_bytes<R>(p.K);
     if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -99,7 +100,26 @@ inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream
     q.inv_gain = p.inv_gain; q.conj_inverse = p.conj_inverse; q.status = dev.status;
     long long grid = dev.sms;
     if (grid > p.rows) grid = p.rows;
+#ifdef TFNO_TC_TRACE
+    static long long* trace_buf = nullptr;
+    if (!trace_buf) cudaMalloc(&trace_buf, sizeof(long long) * 148 * 16 * 12);
+    cudaMemset(trace_buf, 0, sizeof(long long) * 148 * 16 * 12);
+    q.trace = trace_buf;
+#endif
     kernel<<<(unsigned)grid, tc::kTcThreads, smem, st>>>(q);
+#ifdef TFNO_TC_TRACE
+    {
+        cudaDeviceSynchronize();
+        static long long host[148 * 16 * 12];
+        cudaMemcpy(host, trace_buf, sizeof(host), cudaMemcpyDeviceToHost);
+        const char* role[14] = {"F0", "I1", "F2", "I3", "F4", "I5", "F6", "I7", "X8", "X9", "X10", "X11", "PROD", "MMA"};
+        for (int w = 0; w < 14; ++w) {
+            double t[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+            for (int b = 0; b < (int)grid; ++b) for (int k = 0; k < 12; ++k) t[k] += (double)host[(b * 16 + w) * 12 + k] / grid;
+            fprintf(stderr, "trace %-4s total=%8.0f w0=%7.0f w1=%7.0f w2=%7.0f w3=%7.0f load=%7.0f mma=%7.0f fft=%7.0f in=%7.0f mid=%7.0f out=%7.0f\n", role[w], t[0], t[1], t[2], t[3], t[4], t[5], t[6], t[7], t[8], t[9], t[10]);
+        }
+    }
+#endif
     return launch_status();
 }
 
@@ -112,7 +132,10 @@ inline int launch_tile(const DeviceInfo& dev, int len, TileParams p, cudaStream_
     const int R = (FWD || INV) ? len / 64 : 2;      // the pure GEMM instance does not depend on R
     if ((FWD || INV) && !supported_len(len)) return TFNO_ERR_UNSUPPORTED;
     if constexpr (FWD && INV) {
-        if (tc_eligible(dev, len, p)) return len == 128 ? launch_tc_inst<2>(dev, p, st) : launch_tc_inst<4>(dev, p, st);
+        if (tc_eligible(dev, len, p)) {
+            if (p.conj_inverse) return len == 128 ? launch_tc_inst<2, true>(dev, p, st) : launch_tc_inst<4, true>(dev, p, st);
+            return len == 128 ? launch_tc_inst<2, false>(dev, p, st) : launch_tc_inst<4, false>(dev, p, st);
+        }
     }
     const int N = p.N;
     const long long M = p.rows * kModes;

@@ -4,23 +4,33 @@
 // (fusion_variants/1D_D_exp_fused_fft_cgemm_ifft/fused_fft_cgemm_ifft_7.cuh:9-222 in the
 // reference), restricted to N = 64 output channels, K <= 64, DY in {128, 256}.
 //
-// One persistent CTA per SM, 320 threads in four roles that overlap through mbarriers:
+// One persistent CTA per SM, 512 threads in four warpgroups; setmaxnreg moves registers from
+// the two helper warpgroups to the two compute warpgroups (216 each), so that a compute thread
+// can hold a whole 64-point transform in registers:
 //
-//   warp 8      producer   cp.async.bulk of whole input rows (DY*8 bytes each) into a 3-stage
-//                          shared-memory ring, CH = 64/R channels per stage
-//   warps 0-3   forward    two half-teams of 64 threads; a half-team takes one ring stage, each
-//                          group of R lanes transforms one channel (64-point register FFT +
-//                          reduce-scatter), splits the 64 kept modes into tf32 hi/lo parts and
-//                          stores them as the B operand S[mode][kk] (K-major core matrices)
-//   warp 9      MMA        one thread issues tcgen05.mma kind::tf32:
-//                              D[128 x 64 modes] += Wt[128 x 8] * S[8 x 64]
-//                          Wt (the weights, rows 0-63 -> Re, 64-127 -> Im of output channel n,
-//                          columns kk = (chunk, Re|Im part, channel)) lives in tensor memory for
-//                          the whole kernel; fp32 accuracy comes from three tf32 products
-//                          (hi*hi + lo*hi + hi*lo).  Accumulators are double-buffered in TMEM.
-//   warps 4-7   inverse    tcgen05.ld of one accumulator row per thread -> Re/Im planes in shared
-//                          memory -> groups of R lanes run the zero-padded inverse transform of
-//                          one output channel and store it.
+//   warps 0,2,4,6  forward  two half-teams {0,4} and {2,6}.  Input rows (DY*8 bytes each) arrive by
+//                           cp.async.bulk in a 3-stage shared-memory ring, CH = 64/R channels per
+//                           stage; a half-team takes one stage, each group of R lanes transforms
+//                           one channel (64-point register FFT + reduce-scatter), splits the 64
+//                           kept modes into tf32 hi/lo parts and stores them as the B operand
+//                           S[mode][kk] (K-major core matrices).
+//   warps 1,3,5,7  inverse  groups of R lanes read one output channel's 64 modes from the Re/Im
+//                           planes, run the zero-padded inverse transform and store the signal.
+//   warps 8-11     hand-off tcgen05.ld of one accumulator row per thread -> Re/Im planes in shared
+//                           memory (a warp may only touch its own quarter of tensor memory, so
+//                           this needs four warps with distinct warp%4).
+//   warp 12        producer one thread arms a ring stage, CH lanes issue the bulk copies.
+//   warp 13        MMA      one thread issues tcgen05.mma kind::tf32, in chunk order:
+//                               D[128 x 64 modes] += Wt[128 x 8] * S[8 x 64]
+//                           Wt (the weights, rows 0-63 -> Re, 64-127 -> Im of output channel n,
+//                           columns kk = (chunk, Re|Im part, channel)) lives in tensor memory for
+//                           the whole kernel; fp32 accuracy comes from three tf32 products
+//                           (hi*hi + lo*hi + hi*lo).  Accumulators are double-buffered in TMEM.
+//
+// A scheduler partition hosts warps w, w+4, w+8, w+12: its two compute warps have the same role
+// and run in step, and both roles funnel through ONE copy of the unrolled 64-point transform (the
+// inverse is computed as swap(FFT(swap(u)))); together this keeps the instruction stream a
+// partition fetches short.
 //
 // Every wait is bounded: a wait that runs out sets `*status` and an abort flag, all roles leave
 // their loops, tensor memory is released, and the kernel returns.
@@ -31,10 +41,24 @@
 namespace tfno {
 namespace tc {
 
-constexpr int kTcThreads = 320;
+constexpr int kTcThreads = 512;               // 4 warpgroups, see the role table above
 constexpr int kStages = 3;
 constexpr int kLBO = 144;                   // bytes between K-adjacent core matrices of S (128 + 16 pad)
 constexpr uint32_t kSpinLimit = 1u << 22;   // polls (with back-off) before a wait gives up
+
+#ifdef TFNO_TC_TRACE
+#define TFNO_TRACE_DECL long long tr_wait[11] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long tr_t0 = clock64(); long long tr_mark = 0;
+#define TFNO_TRACE_MARK() tr_mark = clock64()
+#define TFNO_TRACE_SINCE(slot) do { long long n_ = clock64(); tr_wait[slot] += n_ - tr_mark; tr_mark = n_; } while (0)
+#define TFNO_TRACE_WAIT(slot, expr) [&]() { long long t_ = clock64(); bool r_ = (expr); tr_wait[slot] += clock64() - t_; return r_; }()
+#define TFNO_TRACE_FLUSH() if (lane == 0 && p.trace) { long long* d_ = p.trace + ((long long)blockIdx.x * 16 + warp) * 12; d_[0] = clock64() - tr_t0; for (int i_ = 0; i_ < 11; ++i_) d_[1 + i_] = tr_wait[i_]; }
+#else
+#define TFNO_TRACE_DECL
+#define TFNO_TRACE_MARK()
+#define TFNO_TRACE_SINCE(slot)
+#define TFNO_TRACE_WAIT(slot, expr) (expr)
+#define TFNO_TRACE_FLUSH()
+#endif
 
 struct TcParams {
     long long rows;
@@ -45,12 +69,19 @@ struct TcParams {
     float2 inv_gain;
     int conj_inverse;
     int* status;                // device-visible word; 0 = ok
+    long long* trace;           // optional per-warp cycle counters (builds with TFNO_TC_TRACE only)
 };
 
-// SBO: bytes between 8-mode groups of S: all K chunks, rounded up to 64 (mod 256) so that lanes
-// holding modes 16 apart fall into different banks
-__host__ __device__ inline int s_sbo(int K) { int span = (2 * K / 4) * kLBO; return ((span + 255) / 256) * 256 + 64; }
-__host__ __device__ inline int s_bytes(int K) { return 8 * s_sbo(K); }           // one of the hi / lo arrays
+// SBO: bytes between 8-mode groups of S.  The R lanes of a group store modes 64/R apart in the
+// same instruction, i.e. 8/R groups apart: SBO is the span of all K chunks rounded up so that
+// (8/R)*SBO is 32 bytes (R = 4) or 64 bytes (R = 2) past a multiple of 128 -- both hold when SBO
+// is 16 past a multiple of 64 -- and the lanes of a warp fall into 32 different banks.
+__host__ __device__ inline int s_sbo(int K, int R) {
+    const int span = (2 * K / 4) * kLBO;
+    (void)R;
+    return ((span + 63) / 64) * 64 + 16;
+}
+__host__ __device__ inline int s_bytes(int K, int R) { return 8 * s_sbo(K, R); }   // one of the hi / lo arrays
 
 template <int R> struct Geometry {
     static constexpr int DY = 64 * R;
@@ -66,7 +97,7 @@ __host__ inline size_t tc_smem_bytes(int K) {
     using G = Geometry<R>;
     size_t b = 0;
     b += (size_t)kStages * G::STAGE_BYTES;        // ring
-    b += 2 * (size_t)s_bytes(K);                  // S hi, S lo
+    b += 2 * (size_t)s_bytes(K, R);               // S hi, S lo
     b += 2 * 64 * 256;                            // Re / Im planes [64 channels][64 modes] fp32
     b += 2 * (size_t)R * 64 * 8;                  // twiddle tables
     b += 256;                                     // barriers, tmem base, abort flag
@@ -152,6 +183,13 @@ __device__ __forceinline__ float tf32_hi(float v) {
     return __uint_as_float(u);
 }
 
+#define TFNO_TMEM_ST8(taddr, r)                                                                            \
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"                     \
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory")
+#define TFNO_TMEM_LD8(taddr, r)                                                                            \
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"                     \
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])  \
+                 : "r"(taddr) : "memory")
 #define TFNO_TMEM_ST16(taddr, r, o)                                                                                      \
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"   \
                  ::"r"(taddr), "r"(r[o + 0]), "r"(r[o + 1]), "r"(r[o + 2]), "r"(r[o + 3]), "r"(r[o + 4]), "r"(r[o + 5]),   \
@@ -168,7 +206,9 @@ __device__ __forceinline__ float tf32_hi(float v) {
 __device__ __forceinline__ int plane_chunk(int n, int c) { return (c & ~7) | ((c & 7) ^ (n & 7)); }
 
 // ---------------------------------------------------------------------------------------------
-template <int R>
+// INVERSE = true: second transform is the true inverse (done as swap(FFT(swap(u))), so that both
+// roles run the same forward 64-point code); false: a second forward transform.
+template <int R, bool INVERSE>
 __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) {
     using G = Geometry<R>;
     constexpr int CH = G::CH;
@@ -176,7 +216,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int K = p.K;
     const int NC = K / CH;                            // chunks per row
-    const int SBO = s_sbo(K), SBYTES = s_bytes(K);
+    const int SBO = s_sbo(K, R), SBYTES = s_bytes(K, R);
     unsigned char* ring = base;
     unsigned char* sS = ring + kStages * G::STAGE_BYTES;            // [hi | lo]
     float* planes = reinterpret_cast<float*>(sS + 2 * SBYTES);      // [2][64][64]
@@ -185,44 +225,57 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
     uint64_t* bars = reinterpret_cast<uint64_t*>(twI + R * 64);
     // barrier indices
     constexpr int B_FULL = 0, B_EMPTY = kStages, B_SFULL = 2 * kStages, B_SEMPTY = B_SFULL + 8, B_AFULL = B_SEMPTY + 8,
-                  B_AEMPTY = B_AFULL + 2, B_COUNT = B_AEMPTY + 2;
+                  B_AEMPTY = B_AFULL + 2, B_PFULL = B_AEMPTY + 2, B_PEMPTY = B_PFULL + 1, B_COUNT = B_PEMPTY + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // Roles.  A scheduler partition hosts warps w, w+4, w+8, w+12; giving it two compute warps of
+    // the SAME role keeps its instruction cache on one role's code.
+    const bool is_compute = warp < 8;
+    const bool is_fwd = is_compute && !(warp & 1);          // warps 0,2,4,6
+    const bool is_inv = is_compute && (warp & 1);           // warps 1,3,5,7
+    const bool is_xfer = warp >= 8 && warp < 12;            // TMEM quarter = warp & 3
 
     // ---------------- set-up ----------------
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 2); }
         for (int c = 0; c < 8; ++c) { mbar_init(bar(B_SFULL + c), 2); mbar_init(bar(B_SEMPTY + c), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar(B_AFULL + b), 1); mbar_init(bar(B_AEMPTY + b), 4); }
+        mbar_init(bar(B_PFULL), 4);
+        mbar_init(bar(B_PEMPTY), 4);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 9) {
+    if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     fill_forward_table<R>(twF, tid, kTcThreads);
-    fill_inverse_table<R>(twI, tid, kTcThreads, p.inv_gain, p.conj_inverse != 0);
+    fill_inverse_table<R>(twI, tid, kTcThreads, p.inv_gain, INVERSE);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t TM_WHI = 0, TM_WLO = 2 * K, TM_ACC = 4 * K;        // column offsets; accumulators 2 x 64 columns
 
-    // weights into tensor memory: thread i of warps 4-7 owns row i = (part_out, n)
-    if (warp >= 4 && warp < 8) {
-        const int i = tid - 128, n = i & 63, im_row = i >> 6;
+    const long long first = blockIdx.x;
+    const int n_it = first < p.rows ? (int)((p.rows - first + gridDim.x - 1) / gridDim.x) : 0;
+    const long long n_loads = (long long)n_it * NC;
+
+    // weights into tensor memory: thread i of warps 8-11 owns row i: rows 0-63 produce Re, rows
+    // 64-127 produce Im of output channel n = i & 63
+    if (is_xfer) {
+        const int i = tid - 256, n = i & 63, im_row = i >> 6;
         const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         for (int c = 0; c < NC; ++c) {
             for (int part = 0; part < 2; ++part) {
-                for (int k0 = 0; k0 < CH; k0 += 16) {
-                    uint32_t hi[16], lo[16];
+                for (int k0 = 0; k0 < CH; k0 += 8) {
+                    uint32_t hi[8], lo[8];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < 8; ++j) {
                         const int k = c * CH + k0 + j;
                         const float2 wv = __ldg(p.w + (long long)k * p.w_stride_k + (long long)n * p.w_stride_n);
                         // Re row: [ Wr | -Wi ],  Im row: [ Wi | Wr ]  against  S = [ Xr ; Xi ]
@@ -232,8 +285,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                         lo[j] = __float_as_uint(tf32_hi(v - h));
                     }
                     const uint32_t col = (uint32_t)(c * 2 * CH + part * CH + k0);
-                    TFNO_TMEM_ST16(trow + TM_WHI + col, hi, 0);
-                    TFNO_TMEM_ST16(trow + TM_WLO + col, lo, 0);
+                    TFNO_TMEM_ST8(trow + TM_WHI + col, hi);
+                    TFNO_TMEM_ST8(trow + TM_WLO + col, lo);
                 }
             }
         }
@@ -243,31 +296,60 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
     __syncthreads();
     tc_fence_after();
 
-    const long long first = blockIdx.x;
-    const int n_it = first < p.rows ? (int)((p.rows - first + gridDim.x - 1) / gridDim.x) : 0;
-
-    if (warp == 8) {
-        // ======================= producer =======================
-        long long L = 0;
-        bool ok = true;
-        for (int it = 0; it < n_it && ok; ++it) {
-            const long long row = first + (long long)it * gridDim.x;
-            for (int c = 0; c < NC && ok; ++c, ++L) {
-                const int s = (int)(L % kStages);
-                const uint32_t u = (uint32_t)(L / kStages);
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(B_EMPTY + s), (u & 1) ^ 1, abort_flag, p.status, 11));
+    TFNO_TRACE_DECL
+    if (!is_compute) {
+        // ============ warpgroups 2 and 3: accumulator hand-off, data movement, MMA issue ============
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+        if (is_xfer) {
+            // accumulator row i = (part, channel) of this thread -> Re / Im planes in shared memory
+            const int i = tid - 256;
+            const int q = warp & 3;
+            float* prow = planes + (i >> 6) * 4096 + (i & 63) * 64;
+            bool ok = true;
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int buf = it & 1;
+                ok = TFNO_TRACE_WAIT(0, mbar_wait(bar(B_AFULL + buf), (it >> 1) & 1, abort_flag, p.status, 41));
+                if (ok) ok = TFNO_TRACE_WAIT(1, mbar_wait(bar(B_PEMPTY), (it & 1) ^ 1, abort_flag, p.status, 42));
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + TM_ACC + 64 * buf;
+#pragma unroll 1
+                for (int c0 = 0; c0 < 64; c0 += 8) {
+                    uint32_t acc[8];
+                    TFNO_TMEM_LD8(taddr + c0, acc);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int cc = c0 >> 2;
+                    *reinterpret_cast<uint4*>(prow + plane_chunk(i & 63, cc) * 4) = make_uint4(acc[0], acc[1], acc[2], acc[3]);
+                    *reinterpret_cast<uint4*>(prow + plane_chunk(i & 63, cc + 1) * 4) = make_uint4(acc[4], acc[5], acc[6], acc[7]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(bar(B_AEMPTY + buf)); mbar_arrive(bar(B_PFULL)); }
+            }
+        } else if (warp == 12) {
+            // producer: keeps the ring full
+            auto issue_load = [&](long long L) {       // whole warp; lanes < CH copy one row each
+                const int s = (int)(L % kStages);
+                const long long row = first + (L / NC) * gridDim.x;
+                const int c = (int)(L % NC);
                 if (lane == 0) mbar_arrive_expect_tx(bar(B_FULL + s), CH * G::ROW_BYTES);
                 __syncwarp();
                 for (int j = lane; j < CH; j += 32) {
                     const float2* src = p.x + row * p.x_stride_row + (long long)(c * CH + j) * p.x_stride_k;
                     bulk_load(smem_u32(ring + s * G::STAGE_BYTES + j * G::ROW_STRIDE), src, G::ROW_BYTES, bar(B_FULL + s));
                 }
+            };
+            bool ok = true;
+            for (long long L = 0; L < n_loads && ok; ++L) {
+                const int s = (int)(L % kStages);
+                const uint32_t u = (uint32_t)(L / kStages);
+                ok = __all_sync(0xffffffffu, TFNO_TRACE_WAIT(0, mbar_wait(bar(B_EMPTY + s), (u & 1) ^ 1, abort_flag, p.status, 11)));
+                if (!ok) break;
+                issue_load(L);
             }
-        }
-    } else if (warp == 9) {
-        // ======================= MMA issuer =======================
-        if (lane == 0) {
+        } else if (warp == 13 && lane == 0) {
+            // MMA issuer
             const uint32_t idesc = make_idesc_tf32(64);
             const uint32_t s_hi = smem_u32(sS), s_lo = s_hi + SBYTES;
             bool ok = true;
@@ -275,13 +357,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 const int buf = it & 1;
                 const uint32_t d_tmem = tmem + TM_ACC + 64 * buf;
                 for (int c = 0; c < NC && ok; ++c) {
-                    ok = mbar_wait(bar(B_SFULL + c), it & 1, abort_flag, p.status, 21);
-                    if (ok && c == 0) ok = mbar_wait(bar(B_AEMPTY + buf), ((it >> 1) & 1) ^ 1, abort_flag, p.status, 22);
+                    ok = TFNO_TRACE_WAIT(0, mbar_wait(bar(B_SFULL + c), it & 1, abort_flag, p.status, 21));
+                    if (ok && c == 0) ok = TFNO_TRACE_WAIT(1, mbar_wait(bar(B_AEMPTY + buf), ((it >> 1) & 1) ^ 1, abort_flag, p.status, 22));
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll 1
                     for (int j = 0; j < G::KSTEPS_PER_CHUNK; ++j) {
-                        const int ks = c * G::KSTEPS_PER_CHUNK + j;               // global k-step: kk in [8ks, 8ks+8)
+                        const int ks = c * G::KSTEPS_PER_CHUNK + j;               // k-step: kk in [8ks, 8ks+8)
                         const uint64_t dhi = make_kmajor_desc(s_hi + 2 * ks * kLBO, kLBO, SBO);
                         const uint64_t dlo = make_kmajor_desc(s_lo + 2 * ks * kLBO, kLBO, SBO);
                         const uint32_t a_hi = tmem + TM_WHI + 8 * ks, a_lo = tmem + TM_WLO + 8 * ks;
@@ -290,40 +372,97 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                         umma_tf32_ts(d_tmem, a_hi, dlo, idesc, 1u);
                     }
                     umma_commit(bar(B_SEMPTY + c));
+                    if (c == NC - 1) umma_commit(bar(B_AFULL + buf));
                 }
-                if (ok) umma_commit(bar(B_AFULL + buf));
             }
         }
-    } else if (warp < 4) {
-        // ======================= forward transform =======================
-        const int half = warp >> 1;                       // half-team: chunks c = half, half+2, ...
-        const int wl = warp & 1;                          // warp inside the half-team
-        constexpr int GPW = 32 / R;                       // channels per warp
-        const int g = lane % GPW, r = lane / GPW;         // lane = g + GPW*r: the R lanes of a group are GPW apart
-        const int kl = wl * GPW + g;                      // channel inside the chunk
-        bool ok = true;
-        for (int it = 0; it < n_it && ok; ++it) {
-            for (int c = half; c < NC && ok; c += 2) {
+    } else {
+    // ======================= forward and inverse warps =======================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;" ::: "memory");
+    constexpr int GPW = 32 / R;                       // groups (channels) per warp
+    const int g = lane % GPW, r = lane / GPW;         // lane = g + GPW*r: the R lanes of a group are GPW apart
+    const int half = (warp >> 1) & 1, wl = warp >> 2; // forward: half-team {0,4} / {2,6} and warp inside it
+    const int kl = wl * GPW + g;                      // forward: channel inside the chunk
+    const int qi = warp >> 1;                         // inverse: 0..3
+    constexpr int GROUPS = 128 / R;                   // inverse: channels per pass
+    const int tasks_per_row = is_fwd ? (NC - half + 1) / 2 : 64 / GROUPS;
+    bool alive = true;
+
+    for (int it = 0; it < n_it && alive; ++it) {
+        const long long row = first + (long long)it * gridDim.x;
+        for (int t = 0; t < tasks_per_row && alive; ++t) {
+            float2 v[64];
+            float sgn = 1.0f;
+            int c = 0, n = 0, s = 0;
+            // ------------------------------ prologue ------------------------------
+            if (is_fwd) {
+                c = half + 2 * t;
                 const long long L = (long long)it * NC + c;
-                const int s = (int)(L % kStages);
+                s = (int)(L % kStages);
                 const uint32_t u = (uint32_t)(L / kStages);
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(B_FULL + s), u & 1, abort_flag, p.status, 31));
-                if (!ok) break;
-                float2 v[64];
+                alive = __all_sync(0xffffffffu, TFNO_TRACE_WAIT(0, mbar_wait(bar(B_FULL + s), u & 1, abort_flag, p.status, 31)));
+                if (!alive) break;
                 const float2* srow = reinterpret_cast<const float2*>(ring + s * G::STAGE_BYTES + kl * G::ROW_STRIDE);
+                TFNO_TRACE_MARK();
 #pragma unroll
-                for (int n = 0; n < 64; ++n) v[n] = srow[R * n + r];
+                for (int i = 0; i < 64; ++i) v[i] = srow[R * i + r];
+                TFNO_TRACE_SINCE(7);
+                sgn = (r & (R >> 1)) ? -1.0f : 1.0f;          // upper half of the group: spectrum rotated by 32
+            } else {
+                if (t == 0) {
+                    alive = __all_sync(0xffffffffu, TFNO_TRACE_WAIT(0, mbar_wait(bar(B_PFULL), it & 1, abort_flag, p.status, 43)));
+                    if (!alive) break;
+                }
+                TFNO_TRACE_MARK();
+                n = t * GROUPS + qi * GPW + g;
+                const float* pre = planes + n * 64;
+                const float* pim = planes + 4096 + n * 64;
+                const float2* tw = twI + 64 * r;
+#pragma unroll
+                for (int cc = 0; cc < 16; ++cc) {
+                    const float4 a = *reinterpret_cast<const float4*>(pre + plane_chunk(n, cc) * 4);
+                    const float4 b = *reinterpret_cast<const float4*>(pim + plane_chunk(n, cc) * 4);
+                    const float4 t0 = *reinterpret_cast<const float4*>(tw + 4 * cc);
+                    const float4 t1 = *reinterpret_cast<const float4*>(tw + 4 * cc + 2);
+                    const float2 u0 = cmul(make_float2(a.x, b.x), make_float2(t0.x, t0.y));
+                    const float2 u1 = cmul(make_float2(a.y, b.y), make_float2(t0.z, t0.w));
+                    const float2 u2 = cmul(make_float2(a.z, b.z), make_float2(t1.x, t1.y));
+                    const float2 u3 = cmul(make_float2(a.w, b.w), make_float2(t1.z, t1.w));
+                    // inverse as swap(FFT(swap(u))): exchange re/im going in (and coming out below)
+                    v[4 * cc] = INVERSE ? make_float2(u0.y, u0.x) : u0;
+                    v[4 * cc + 1] = INVERSE ? make_float2(u1.y, u1.x) : u1;
+                    v[4 * cc + 2] = INVERSE ? make_float2(u2.y, u2.x) : u2;
+                    v[4 * cc + 3] = INVERSE ? make_float2(u3.y, u3.x) : u3;
+                }
+                TFNO_TRACE_SINCE(8);
+            }
+
+            // ------------------------------ the one 64-point transform ------------------------------
+            TFNO_TRACE_WAIT(6, (fft64<-1>(v, sgn), true));
+
+            // ------------------------------ epilogue ------------------------------
+            if (is_fwd) {
+                // every input sample has been consumed by now: hand the ring stage back
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_EMPTY + s));
-                // 64-point transforms + twiddles, then the reduce-scatter over the R lanes (GPW apart)
-                forward_local<R>(v, twF + 64 * r, r);
+                const float2* tw = twF + 64 * r;
+                TFNO_TRACE_MARK();
+#pragma unroll
+                for (int j = 0; j < 64; j += 2) {
+                    const float4 tt = *reinterpret_cast<const float4*>(tw + j);
+                    v[slot(j)] = cmul(v[slot(j)], make_float2(tt.x, tt.y));
+                    v[slot(j + 1)] = cmul(v[slot(j + 1)], make_float2(tt.z, tt.w));
+                }
+                // reduce-scatter over the R lanes of the group (GPW apart)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[slot(j)] = cadd(v[slot(j)], shfl_xor2(v[slot(32 + j)], (R >> 1) * GPW));
                 if constexpr (R >= 4) exchange_round<16>(v, (R >> 2) * GPW, (r & (R >> 2)) != 0);
                 // lane r now holds modes 64/R*r + j, j < 64/R, in v[slot(j)]
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(B_SEMPTY + c), (it & 1) ^ 1, abort_flag, p.status, 32));
-                if (!ok) break;
+                TFNO_TRACE_SINCE(8);
+                alive = __all_sync(0xffffffffu, TFNO_TRACE_WAIT(1, mbar_wait(bar(B_SEMPTY + c), (it & 1) ^ 1, abort_flag, p.status, 32)));
+                if (!alive) break;
                 constexpr int PER = 64 / R;
+                TFNO_TRACE_MARK();
                 const int kk_re = c * 2 * CH + kl, kk_im = kk_re + CH;
                 unsigned char* hi_re = sS + (kk_re >> 2) * kLBO + (kk_re & 3) * 4;
                 unsigned char* hi_im = sS + (kk_im >> 2) * kLBO + (kk_im & 3) * 4;
@@ -341,70 +480,31 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_SFULL + c));
-            }
-        }
-    } else {
-        // ======================= inverse transform =======================
-        const int i = tid - 128;                          // accumulator row: part = i >> 6, channel n = i & 63
-        const int q = warp & 3;
-        constexpr int GROUPS = 128 / R;                   // channels per pass
-        constexpr int GPW = 32 / R;
-        const int g = lane % GPW, j1 = lane / GPW;
-        const int ch_in_pass = q * GPW + g;
-        bool ok = true;
-        (void)ok;
-        for (int it = 0; it < n_it; ++it) {
-            const long long row = first + (long long)it * gridDim.x;
-            const int buf = it & 1;
-            ok = mbar_wait(bar(B_AFULL + buf), (it >> 1) & 1, abort_flag, p.status, 41);
-            // one answer for the whole team: nobody may be left alone at a later named barrier
-            if (named_barrier_any(1, 128, !ok)) break;
-            tc_fence_after();
-            {
-                uint32_t acc[64];
-                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + TM_ACC + 64 * buf;
-                TFNO_TMEM_LD16(taddr + 0, acc, 0);
-                TFNO_TMEM_LD16(taddr + 16, acc, 16);
-                TFNO_TMEM_LD16(taddr + 32, acc, 32);
-                TFNO_TMEM_LD16(taddr + 48, acc, 48);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_AEMPTY + buf));
-                float* prow = planes + (i >> 6) * 4096 + (i & 63) * 64;
-#pragma unroll
-                for (int c = 0; c < 16; ++c)
-                    *reinterpret_cast<uint4*>(prow + plane_chunk(i & 63, c) * 4) =
-                        make_uint4(acc[4 * c], acc[4 * c + 1], acc[4 * c + 2], acc[4 * c + 3]);
-            }
-            named_barrier(2, 128);
-#pragma unroll 1
-            for (int n0 = 0; n0 < 64; n0 += GROUPS) {
-                const int n = n0 + ch_in_pass;
-                float2 v[64];
-                const float* pre = planes + n * 64;
-                const float* pim = planes + 4096 + n * 64;
-#pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const float4 a = *reinterpret_cast<const float4*>(pre + plane_chunk(n, c) * 4);
-                    const float4 b = *reinterpret_cast<const float4*>(pim + plane_chunk(n, c) * 4);
-                    v[4 * c] = make_float2(a.x, b.x); v[4 * c + 1] = make_float2(a.y, b.y);
-                    v[4 * c + 2] = make_float2(a.z, b.z); v[4 * c + 3] = make_float2(a.w, b.w);
+                TFNO_TRACE_SINCE(9);
+            } else {
+                if (t == tasks_per_row - 1) {
+                    // the planes have been read for the last time this row (values are in use above)
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(B_PEMPTY));
                 }
-                if (n0 + GROUPS >= 64) named_barrier(3, 128);      // planes may be overwritten from here on
-                if (p.conj_inverse) inverse_pad_lane<+1>(v, twI + 64 * j1);
-                else inverse_pad_lane<-1>(v, twI + 64 * j1);
                 float2* dst = p.y + row * p.y_stride_row + (long long)n * p.y_stride_n;
+                TFNO_TRACE_MARK();
 #pragma unroll
-                for (int j2 = 0; j2 < 64; ++j2) dst[R * j2 + j1] = v[slot(j2)];
+                for (int j2 = 0; j2 < 64; ++j2) {
+                    const float2 o = v[slot(j2)];
+                    dst[R * j2 + r] = INVERSE ? make_float2(o.y, o.x) : o;
+                }
+                TFNO_TRACE_SINCE(9);
             }
         }
     }
+    }   // forward / inverse warps
 
     // ---------------- teardown ----------------
+    TFNO_TRACE_FLUSH();
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
     }
 }
