@@ -39,7 +39,8 @@ typedef enum {
     TFNO_ERR_CUDA = 3,          /* a CUDA runtime call or kernel launch failed                    */
     TFNO_ERR_ALLOC = 4,         /* host or device allocation failed                               */
     TFNO_ERR_LIBRARY = 5,       /* cuFFT / cuBLAS failure (variant E only)                        */
-    TFNO_ERR_WORKSPACE = 6      /* workspace missing or smaller than tfno_workspace_bytes()       */
+    TFNO_ERR_WORKSPACE = 6,     /* workspace missing or smaller than tfno_workspace_bytes()       */
+    TFNO_ERR_SCRATCH_LIMIT = 7  /* tfno_spectral_conv2d_static: problem exceeds the static scratch */
 } tfno_status;
 
 /* Fusion variants, named after the reference executables TurboFNO_{1D,2D}_{A..E}
@@ -157,6 +158,35 @@ int tfno_fft_stride(tfno_handle* h, int log2_len, const void* in, void* out, int
  * (fusion_variants/2D_A_exp_fft+cgemm+ifft/fused_trunc_2D.cu:35,219) */
 int tfno_ifft_stride(tfno_handle* h, int log2_len, const void* in, void* out, int DY, long long total_columns,
                      void* stream);
+
+/* ---- allocation-free 2D layer ---------------------------------------------------------------------
+ * This entry point has no counterpart in the reference.
+ *
+ * It is for callers that are not allowed to allocate device memory when they run a layer and have
+ * no scratch buffer to pass to tfno_exec: code running inside an arena or memory-pool scheme that
+ * already owns the whole device, pipelines whose rules forbid allocation after start-up, and
+ * plug-ins called between another framework's allocator operations, where a cudaMalloc would
+ * force a device-wide synchronisation.  It computes one 2D spectral-convolution layer (FNO
+ * semantics: alpha * contraction, true inverse, 1/(DX*DY)) in the reference layout
+ * x[K][bs][DX][DY], w[k + n*K], y[N][bs][DX][DY], exactly like a variant-D tfno_exec, but takes its
+ * two spectrum buffers from a fixed 64 MiB device array inside the library image.  Every GPU that
+ * loads the library carries that array until the process exits.
+ *
+ *   - no cudaMalloc / cudaFree / allocating library call is made, on any call
+ *   - limit: 8*4096*bs*(K + N) bytes (each term rounded up to 256) must fit in
+ *     tfno_static_scratch_bytes(); larger problems return TFNO_ERR_SCRATCH_LIMIT and do nothing
+ *   - DX, DY in {128, 256}; K a multiple of 8, N a multiple of 64; 16-byte aligned pointers
+ *   - runs on the CURRENT device, asynchronously on `stream`
+ *   - the first call on a device looks up the array's device address and the device limits
+ *     (host-side work only); make that first call before starting any stream capture, and not
+ *     from two threads at once
+ *   - all calls on a device share the one array: two calls that can overlap on the GPU (different
+ *     streams without an ordering between them) race on it.  Calls on one stream are safe, and
+ *     nothing in the array needs clearing between calls.
+ */
+size_t tfno_static_scratch_bytes(void);
+int tfno_spectral_conv2d_static(long long bs, int DX, int DY, int K, int N, const void* x, const void* w,
+                                void* y, float alpha_re, float alpha_im, void* stream);
 
 #ifdef __cplusplus
 }

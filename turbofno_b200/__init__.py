@@ -18,4 +18,5 @@ from .api import (  # noqa: F401
     fused_fft_cgemm_ifft,
     ifft_stride,
     ifft_stride_DY,
+    spectral_conv2d_static,
 )

@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(_PKG, "libturbofno_b200.so")
 
 OK = 0
 ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_ALLOC, ERR_LIBRARY, ERR_WORKSPACE = 1, 2, 3, 4, 5, 6
+ERR_SCRATCH_LIMIT = 7
 VARIANT = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
 
 
@@ -62,6 +63,8 @@ SYMBOLS = {
     "tfno_ifft_stride_DY": (_i, [_vp, _i, _vp, _vp, _ll, _vp]),
     "tfno_fft_stride": (_i, [_vp, _i, _vp, _vp, _i, _ll, _vp]),
     "tfno_ifft_stride": (_i, [_vp, _i, _vp, _vp, _i, _ll, _vp]),
+    "tfno_static_scratch_bytes": (ctypes.c_size_t, []),
+    "tfno_spectral_conv2d_static": (_i, [_ll, _i, _i, _i, _i, _vp, _vp, _vp, _f, _f, _vp]),
 }
 
 _LIB = None

@@ -210,3 +210,24 @@ def ifft_stride(inp, out, DY, total_columns, DX, stream=None):
     h = Handle.get(inp.device.index)
     check(h.lib.tfno_ifft_stride(h._h, _log2(DX), _ptr(inp), _ptr(out), DY, total_columns, _stream_ptr(stream)), "tfno_ifft_stride")
     return out
+
+
+def spectral_conv2d_static(x, w, y=None, alpha=1 + 0j, stream=None):
+    """One 2D layer through tfno_spectral_conv2d_static: no device allocation is made inside the
+    library, the spectrum scratch lives in a fixed 64 MiB array of the library image.  For hosts
+    that may not allocate when a layer runs (arena-owned devices, no-allocation-after-start-up
+    rules, calls in between another allocator's operations).  x[K, bs, DX, DY], w[N, K] in the
+    reference layout; y is allocated here by torch only if the caller does not pass one."""
+    _check_tensor(x, "x")
+    _check_tensor(w, "w")
+    K, bs, DX, DY = x.shape
+    N = w.shape[0]
+    if y is None:
+        y = torch.empty((N, bs, DX, DY), dtype=torch.complex64, device=x.device)
+    _check_tensor(y, "y")
+    lib = _lib.load()
+    a = complex(alpha)
+    with torch.cuda.device(x.device):
+        check(lib.tfno_spectral_conv2d_static(bs, DX, DY, K, N, _ptr(x), _ptr(w), _ptr(y), a.real, a.imag,
+                                              _stream_ptr(stream)), "tfno_spectral_conv2d_static")
+    return y

@@ -117,6 +117,7 @@ const char* tfno_status_string(int status) {
         case TFNO_ERR_ALLOC: return "allocation failed";
         case TFNO_ERR_LIBRARY: return "cuFFT or cuBLAS call failed";
         case TFNO_ERR_WORKSPACE: return "workspace pointer missing";
+        case TFNO_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the library's static 64 MiB array holds";
     }
     return "unknown status";
 }
@@ -638,6 +639,98 @@ int tfno_fft_stride(tfno_handle* h, int log2_len, const void* in, void* out, int
 }
 int tfno_ifft_stride(tfno_handle* h, int log2_len, const void* in, void* out, int DY, long long total_columns, void* stream) {
     return stage_cols(h, log2_len, in, out, DY, total_columns, false, stream);
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free 2D layer
+//
+// Some hosts of this library may not allocate device memory at the point where they run a layer:
+// code inside a memory-pool or arena scheme that owns every byte of the device and hands none
+// back, real-time / safety-reviewed pipelines that forbid allocation after start-up, and callers
+// that sit between another framework's allocator calls where an extra cudaMalloc would
+// synchronise the device.  tfno_exec already allocates nothing, but the 2D path needs two
+// spectrum-sized scratch buffers that those callers cannot provide.  This entry point keeps the
+// scratch in a fixed device array that is part of the library image.
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = (size_t)64 << 20;     // 64 MiB per GPU that loads the library
+static __device__ __align__(256) unsigned char tfno_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxStaticDevices = 64;
+struct StaticDevice {
+    bool ready;
+    unsigned char* scratch;     // device address of tfno_static_scratch on this device
+    DeviceInfo dev;
+};
+StaticDevice g_static_devices[kMaxStaticDevices];   // zero-initialised, no heap
+
+// once per device, with that device current: resolve the array's DEVICE address (the symbol's
+// name in host code is only a host-side handle) and read the launch limits
+int static_device_setup(int device, StaticDevice** out) {
+    if (device < 0 || device >= kMaxStaticDevices) return TFNO_ERR_INVALID_ARG;
+    StaticDevice& sd = g_static_devices[device];
+    if (!sd.ready) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, tfno_static_scratch) != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return TFNO_ERR_CUDA;
+        }
+        sd.scratch = static_cast<unsigned char*>(ptr);
+        sd.dev = DeviceInfo();
+        sd.dev.device = device;
+        sd.dev.use_tensor_cores = false;
+        if (cudaDeviceGetAttribute(&sd.dev.sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sd.dev.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess) {
+            cudaGetLastError();
+            return TFNO_ERR_CUDA;
+        }
+        sd.ready = true;
+    }
+    *out = &sd;
+    return TFNO_OK;
+}
+
+}  // namespace
+
+size_t tfno_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int tfno_spectral_conv2d_static(long long bs, int DX, int DY, int K, int N, const void* x, const void* w, void* y,
+                                float alpha_re, float alpha_im, void* stream) {
+    if (!x || !w || !y || bs <= 0 || K <= 0 || N <= 0) return TFNO_ERR_INVALID_ARG;
+    if (!aligned16(x) || !aligned16(w) || !aligned16(y)) return TFNO_ERR_INVALID_ARG;
+    if ((DX != 128 && DX != 256) || (DY != 128 && DY != 256) || K % kSlabK != 0 || N % 64 != 0) return TFNO_ERR_UNSUPPORTED;
+    const size_t spec_in = align_up(sizeof(float2) * (size_t)K * (size_t)bs * kModes * kModes);
+    const size_t spec_out = align_up(sizeof(float2) * (size_t)N * (size_t)bs * kModes * kModes);
+    if (spec_in + spec_out > kStaticScratchBytes) return TFNO_ERR_SCRATCH_LIMIT;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) { cudaGetLastError(); return TFNO_ERR_CUDA; }
+    StaticDevice* sd = nullptr;
+    int rc = static_device_setup(device, &sd);
+    if (rc != TFNO_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float2* S = reinterpret_cast<float2*>(sd->scratch);
+    float2* C = reinterpret_cast<float2*>(sd->scratch + spec_in);
+    const long long img = (long long)DX * DY;
+
+    // image transform, channel contraction, image inverse: the same three kernels tfno_exec runs
+    // for a 2D variant-D plan.  Every scratch element that is read has been written by the
+    // preceding kernel of this call (beta = 0), so nothing has to start at zero.
+    ImageParams fi{};
+    fi.nimg = K * bs; fi.per_k = bs; fi.in = static_cast<const float2*>(x); fi.out = S; fi.stride_b = img; fi.stride_k = bs * img;
+    rc = launch_fft2d(sd->dev, DX, DY, fi, false, st);
+    if (rc != TFNO_OK) return rc;
+    TileParams t{};
+    t.rows = bs * kModes; t.K = K; t.N = N;
+    t.x = S; t.w = static_cast<const float2*>(w); t.w_stride_k = 1; t.w_stride_n = K; t.y = C;
+    t.alpha = f2(alpha_re, alpha_im); t.beta = f2(0.f, 0.f); t.conj_inverse = 1;
+    rc = launch_tile<false, false>(sd->dev, DY, t, st);
+    if (rc != TFNO_OK) return rc;
+    ImageParams ii{};
+    ii.nimg = N * bs; ii.per_k = bs; ii.in = C; ii.out = static_cast<float2*>(y); ii.stride_b = img; ii.stride_k = bs * img;
+    ii.gain = f2(1.0f / ((float)DX * (float)DY), 0.f); ii.conj_inverse = 1;
+    return launch_fft2d(sd->dev, DX, DY, ii, true, st);
 }
 
 }  // extern "C"
