@@ -23,7 +23,7 @@ static double check_forward() {
     static float2 v[R][64];
     for (int r = 0; r < R; ++r) {
         for (int n = 0; n < 64; ++n) v[r][n] = make_float2((float)x[R * n + r].real(), (float)x[R * n + r].imag());
-        forward_local<R>(v[r], twF.data() + 64 * r, r);
+        forward_local<R>(v[r], twF.data(), r);
     }
     // exchange rounds, as in forward_trunc()
     float2 t[R][64];
@@ -60,7 +60,7 @@ static double check_inverse(bool conj) {
     for (int j1 = 0; j1 < R; ++j1) {
         float2 v[64];
         for (int m = 0; m < 64; ++m) v[m] = make_float2((float)c[m].real(), (float)c[m].imag());
-        if (conj) inverse_pad_lane<+1>(v, twI.data() + 64 * j1); else inverse_pad_lane<-1>(v, twI.data() + 64 * j1);
+        if (conj) inverse_pad_lane<+1, R>(v, twI.data(), j1); else inverse_pad_lane<-1, R>(v, twI.data(), j1);
         for (int j2 = 0; j2 < 64; ++j2) {
             int j = R * j2 + j1;
             cd ref = 0;

@@ -224,13 +224,19 @@ TFNO_HD float2 unit_root(int e, int n, float sign) {
     return make_float2(cs, sn);
 }
 
+// Table layout: the entries of mode pair (j, j+1) of the R lanes are adjacent -- element (r, j)
+// sits at ((j/2)*R + r)*2 + (j&1) -- so that the R lanes of a group, which read the same pair in
+// the same instruction, fetch one contiguous R*16-byte piece instead of R pieces in one bank.
+template <int R>
+TFNO_HD constexpr int tw_index(int r, int j) { return ((j >> 1) * R + r) * 2 + (j & 1); }
+
 template <int R>
 TFNO_HD void fill_forward_table(float2* twF, int tid, int nthreads) {
     constexpr int DY = 64 * R;
     for (int i = tid; i < R * 64; i += nthreads) {
         int r = i >> 6, j = i & 63;
         int k = (j + ((r & (R >> 1)) ? 32 : 0)) & 63;
-        twF[i] = unit_root((r * k) & (DY - 1), DY, -1.0f);
+        twF[tw_index<R>(r, j)] = unit_root((r * k) & (DY - 1), DY, -1.0f);
     }
 }
 
@@ -239,19 +245,19 @@ TFNO_HD void fill_inverse_table(float2* twI, int tid, int nthreads, float2 g, bo
     constexpr int DY = 64 * R;
     for (int i = tid; i < R * 64; i += nthreads) {
         int j1 = i >> 6, m = i & 63;
-        twI[i] = cmul(g, unit_root((j1 * m) & (DY - 1), DY, conj ? 1.0f : -1.0f));
+        twI[tw_index<R>(j1, m)] = cmul(g, unit_root((j1 * m) & (DY - 1), DY, conj ? 1.0f : -1.0f));
     }
 }
 
 // Lane-local part of the forward transform: 64-point transform of the lane's decimated
 // samples (rotated by 32 on the upper half of the group) and the W_DY^{rk} twiddles.
 template <int R>
-TFNO_HD void forward_local(float2 (&v)[64], const float2* __restrict__ twF_r, int r) {
+TFNO_HD void forward_local(float2 (&v)[64], const float2* __restrict__ twF, int r) {
     const bool hi = (r & (R >> 1)) != 0;
     fft64<-1>(v, hi ? -1.0f : 1.0f);
 #pragma unroll
     for (int j = 0; j < 64; j += 2) {
-        float4 t = *reinterpret_cast<const float4*>(twF_r + j);
+        float4 t = *reinterpret_cast<const float4*>(twF + tw_index<R>(r, j));
         v[slot(j)] = cmul(v[slot(j)], make_float2(t.x, t.y));
         v[slot(j + 1)] = cmul(v[slot(j + 1)], make_float2(t.z, t.w));
     }
@@ -264,26 +270,41 @@ TFNO_D float2 shfl_xor2(float2 a, int mask) {
 
 // One reduce-scatter round over 2*LEN live entries: lanes with `up` keep entries LEN..2*LEN-1,
 // the others keep 0..LEN-1; the other half goes to the partner lane (lane ^ mask).
+// Written as three passes over the registers -- arrange, shuffle IN PLACE, add -- so that all
+// shuffles of a round are independent and in flight together; fused into one loop the compiler,
+// short of registers, serialises shuffle and add and every element pays the full shuffle latency.
 template <int LEN>
 TFNO_D void exchange_round(float2 (&v)[64], int mask, bool up) {
 #pragma unroll
     for (int j = 0; j < LEN; ++j) {
-        float2 lo = v[slot(j)], hi = v[slot(LEN + j)];
-        float2 keep = up ? hi : lo, send = up ? lo : hi;
-        v[slot(j)] = cadd(keep, shfl_xor2(send, mask));
+        const float2 lo = v[slot(j)], hi = v[slot(LEN + j)];
+        v[slot(j)] = up ? hi : lo;            // keep
+        v[slot(LEN + j)] = up ? lo : hi;      // send
     }
+#pragma unroll
+    for (int j = 0; j < LEN; ++j) v[slot(LEN + j)] = shfl_xor2(v[slot(LEN + j)], mask);
+#pragma unroll
+    for (int j = 0; j < LEN; ++j) v[slot(j)] = cadd(v[slot(j)], v[slot(LEN + j)]);
+}
+
+// First round (partner differs in the top lane bit): the rotation by 32 done inside fft64 has
+// already put the kept half into slots 0..31 and the half to send into slots 32..63.
+TFNO_D void exchange_round_top(float2 (&v)[64], int mask) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[slot(32 + j)] = shfl_xor2(v[slot(32 + j)], mask);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[slot(j)] = cadd(v[slot(j)], v[slot(32 + j)]);
 }
 
 // Forward transform of one signal by R adjacent lanes, truncated to 64 modes.
 //   v[n]   : sample R*n + r of the signal (r = lane index within the group)
-//   twF_r  : this lane's row of the forward table
+//   twF    : the forward table (fill_forward_table<R>)
 // On return lane r holds modes 64/R*r + j, j < 64/R, in v[slot(j)].
 template <int R>
-TFNO_D void forward_trunc(float2 (&v)[64], const float2* __restrict__ twF_r, int r) {
-    forward_local<R>(v, twF_r, r);
+TFNO_D void forward_trunc(float2 (&v)[64], const float2* __restrict__ twF, int r) {
+    forward_local<R>(v, twF, r);
     // round 1 (partner R/2): slots j<32 keep, slots 32+j go to the partner
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[slot(j)] = cadd(v[slot(j)], shfl_xor2(v[slot(32 + j)], R >> 1));
+    exchange_round_top(v, R >> 1);
     // further rounds: conditional swap so that the kept half sits in the low slots
     if constexpr (R >= 4) exchange_round<16>(v, R >> 2, (r & (R >> 2)) != 0);
     if constexpr (R >= 8) exchange_round<8>(v, R >> 3, (r & (R >> 3)) != 0);
@@ -292,13 +313,13 @@ TFNO_D void forward_trunc(float2 (&v)[64], const float2* __restrict__ twF_r, int
 #endif
 
 // Inverse transform by one lane of a group of R: in v[m] = mode m (m<64); out: sample
-// R*j2 + j1 in v[slot(j2)].  twI_j1 = this lane's row of the inverse table.
+// R*j2 + j1 in v[slot(j2)].  twI = the inverse table (fill_inverse_table<R>).
 // CONJ = +1 for a true inverse, -1 for a second forward transform.
-template <int CONJ>
-TFNO_HD void inverse_pad_lane(float2 (&v)[64], const float2* __restrict__ twI_j1) {
+template <int CONJ, int R>
+TFNO_HD void inverse_pad_lane(float2 (&v)[64], const float2* __restrict__ twI, int j1) {
 #pragma unroll
     for (int m = 0; m < 64; m += 2) {
-        float4 t = *reinterpret_cast<const float4*>(twI_j1 + m);
+        float4 t = *reinterpret_cast<const float4*>(twI + tw_index<R>(j1, m));
         v[m] = cmul(v[m], make_float2(t.x, t.y));
         v[m + 1] = cmul(v[m + 1], make_float2(t.z, t.w));
     }

@@ -116,7 +116,7 @@ inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream
         for (int w = 0; w < 14; ++w) {
             double t[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
             for (int b = 0; b < (int)grid; ++b) for (int k = 0; k < 12; ++k) t[k] += (double)host[(b * 16 + w) * 12 + k] / grid;
-            fprintf(stderr, "trace %-4s total=%8.0f w0=%7.0f w1=%7.0f w2=%7.0f w3=%7.0f load=%7.0f mma=%7.0f fft=%7.0f in=%7.0f mid=%7.0f out=%7.0f\n", role[w], t[0], t[1], t[2], t[3], t[4], t[5], t[6], t[7], t[8], t[9], t[10]);
+            fprintf(stderr, "trace %-4s total=%8.0f w0=%7.0f w1=%7.0f w2=%7.0f w3=%7.0f load=%7.0f mma=%7.0f fft=%7.0f in=%7.0f mid=%7.0f out=%7.0f loop=%7.0f\n", role[w], t[0], t[1], t[2], t[3], t[4], t[5], t[6], t[7], t[8], t[9], t[10], t[11]);
         }
     }
 #endif

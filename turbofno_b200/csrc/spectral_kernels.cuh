@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(kThreads, 1) spectral_tile_kernel(TileParams p
                 const int k = live ? k0 + g : K - 1;
                 float2 v[64];
                 load_decimated<R>(v, p.x + row * p.x_stride_row + (long long)k * p.x_stride_k, 1, r);
-                forward_trunc<R>(v, twF + 64 * r, r);
+                forward_trunc<R>(v, twF, r);
                 if (live) store_modes_to_tile<R>(v, sA, k, r);
             }
         } else {
@@ -222,8 +222,8 @@ __global__ void __launch_bounds__(kThreads, 1) spectral_tile_kernel(TileParams p
                         v[2 * c] = make_float2(q.x, q.y);
                         v[2 * c + 1] = make_float2(q.z, q.w);
                     }
-                    if (p.conj_inverse) inverse_pad_lane<+1>(v, twI + 64 * j1);
-                    else inverse_pad_lane<-1>(v, twI + 64 * j1);
+                    if (p.conj_inverse) inverse_pad_lane<+1, R>(v, twI, j1);
+                    else inverse_pad_lane<-1, R>(v, twI, j1);
                     store_decimated<R>(v, p.y + row * p.y_stride_row + (long long)n * p.y_stride_n, 1, j1);
                 }
             }
@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1) fft_rows_trunc_kernel(RowsParams 
         if (!live) s = p.nsig - 1;
         float2 v[64];
         load_decimated<R>(v, p.in + (s % p.per_k) * p.stride_row + (s / p.per_k) * p.stride_k, 1, r);
-        forward_trunc<R>(v, twF + 64 * r, r);
+        forward_trunc<R>(v, twF, r);
         if (live) {
             float2* dst = p.out + s * kModes + PER * r;
 #pragma unroll
@@ -316,8 +316,8 @@ __global__ void __launch_bounds__(kThreads, 1) ifft_rows_pad_kernel(RowsParams p
             v[2 * c] = make_float2(q.x, q.y);
             v[2 * c + 1] = make_float2(q.z, q.w);
         }
-        if (p.conj_inverse) inverse_pad_lane<+1>(v, twI + 64 * j1);
-        else inverse_pad_lane<-1>(v, twI + 64 * j1);
+        if (p.conj_inverse) inverse_pad_lane<+1, R>(v, twI, j1);
+        else inverse_pad_lane<-1, R>(v, twI, j1);
         store_decimated<R>(v, p.out + (s % p.per_k) * p.stride_row + (s / p.per_k) * p.stride_k, 1, j1);
     }
 }
@@ -354,7 +354,7 @@ __global__ void __launch_bounds__(kThreads, 1) fft_cols_trunc_kernel(ColsParams 
         const int col = (int)(c % p.DY);
         float2 v[64];
         load_decimated<R>(v, p.in + (img % p.per_k) * p.stride_b + (img / p.per_k) * p.stride_k + col, p.DY, r);
-        forward_trunc<R>(v, twF + 64 * r, r);
+        forward_trunc<R>(v, twF, r);
         if (live) {
             float2* dst = p.out + img * (long long)kModes * p.DY + col;
 #pragma unroll
@@ -382,8 +382,8 @@ __global__ void __launch_bounds__(kThreads, 1) ifft_cols_pad_kernel(ColsParams p
         const float2* src = p.in + img * (long long)kModes * p.DY + col;
 #pragma unroll
         for (int m = 0; m < 64; ++m) v[m] = __ldg(src + (long long)m * p.DY);
-        if (p.conj_inverse) inverse_pad_lane<+1>(v, twI + 64 * j1);
-        else inverse_pad_lane<-1>(v, twI + 64 * j1);
+        if (p.conj_inverse) inverse_pad_lane<+1, R>(v, twI, j1);
+        else inverse_pad_lane<-1, R>(v, twI, j1);
         store_decimated<R>(v, p.out + (img % p.per_k) * p.stride_b + (img / p.per_k) * p.stride_k + col, p.DY, j1);
     }
 }
@@ -424,7 +424,7 @@ __global__ void __launch_bounds__(kThreads, 1) fft2d_trunc_kernel(ImageParams p)
                 const int x = x0 + g;
                 float2 v[64];
                 load_decimated<RY>(v, src + (long long)x * DY, 1, r);
-                forward_trunc<RY>(v, twY + 64 * r, r);
+                forward_trunc<RY>(v, twY, r);
                 store_modes_to_tile<RY>(v, sY, x, r);
             }
         }
@@ -440,7 +440,7 @@ __global__ void __launch_bounds__(kThreads, 1) fft2d_trunc_kernel(ImageParams p)
                 float2 v[64];
 #pragma unroll
                 for (int n = 0; n < 64; ++n) v[n] = sY[tile_index(RX * n + r, ky)];
-                forward_trunc<RX>(v, twX + 64 * r, r);
+                forward_trunc<RX>(v, twX, r);
 #pragma unroll
                 for (int j = 0; j < PER; ++j) dst[(PER * r + j) * kModes + ky] = v[slot(j)];
             }
@@ -474,8 +474,8 @@ __global__ void __launch_bounds__(kThreads, 1) ifft2d_pad_kernel(ImageParams p) 
                 float2 v[64];
 #pragma unroll
                 for (int m = 0; m < 64; ++m) v[m] = __ldg(src + m * kModes + ky);
-                if (p.conj_inverse) inverse_pad_lane<+1>(v, twX + 64 * j1);
-                else inverse_pad_lane<-1>(v, twX + 64 * j1);
+                if (p.conj_inverse) inverse_pad_lane<+1, RX>(v, twX, j1);
+                else inverse_pad_lane<-1, RX>(v, twX, j1);
 #pragma unroll
                 for (int j2 = 0; j2 < 64; ++j2) sY[tile_index(RX * j2 + j1, ky)] = v[slot(j2)];
             }
@@ -494,8 +494,8 @@ __global__ void __launch_bounds__(kThreads, 1) ifft2d_pad_kernel(ImageParams p) 
                     v[2 * c] = make_float2(q.x, q.y);
                     v[2 * c + 1] = make_float2(q.z, q.w);
                 }
-                if (p.conj_inverse) inverse_pad_lane<+1>(v, twY + 64 * j1);
-                else inverse_pad_lane<-1>(v, twY + 64 * j1);
+                if (p.conj_inverse) inverse_pad_lane<+1, RY>(v, twY, j1);
+                else inverse_pad_lane<-1, RY>(v, twY, j1);
                 store_decimated<RY>(v, dst + (long long)x * DY, 1, j1);
             }
         }

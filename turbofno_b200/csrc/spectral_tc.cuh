@@ -45,10 +45,15 @@ constexpr int kTcThreads = 512;               // 4 warpgroups, see the role tabl
 constexpr int kStages = 3;
 constexpr int kLBO = 144;                   // bytes between K-adjacent core matrices of S (128 + 16 pad)
 constexpr uint32_t kSpinLimit = 1u << 22;   // polls (with back-off) before a wait gives up
+#ifndef TFNO_HELPER_IDLE_NS
+#define TFNO_HELPER_IDLE_NS 200
+#endif
+constexpr unsigned kHelperIdleNs = TFNO_HELPER_IDLE_NS;   // sleep between polls of the helper warps
 
 #ifdef TFNO_TC_TRACE
 #define TFNO_TRACE_DECL long long tr_wait[11] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long tr_t0 = clock64(); long long tr_mark = 0;
 #define TFNO_TRACE_MARK() tr_mark = clock64()
+#define TFNO_TRACE_STEP(slot, expr) [&]() { bool r_ = (expr); long long n_ = clock64(); tr_wait[slot] += n_ - tr_mark; tr_mark = n_; return r_; }()
 #define TFNO_TRACE_SINCE(slot) do { long long n_ = clock64(); tr_wait[slot] += n_ - tr_mark; tr_mark = n_; } while (0)
 #define TFNO_TRACE_WAIT(slot, expr) [&]() { long long t_ = clock64(); bool r_ = (expr); tr_wait[slot] += clock64() - t_; return r_; }()
 #define TFNO_TRACE_FLUSH() if (lane == 0 && p.trace) { long long* d_ = p.trace + ((long long)blockIdx.x * 16 + warp) * 12; d_[0] = clock64() - tr_t0; for (int i_ = 0; i_ < 11; ++i_) d_[1 + i_] = tr_wait[i_]; }
@@ -56,6 +61,7 @@ constexpr uint32_t kSpinLimit = 1u << 22;   // polls (with back-off) before a wa
 #define TFNO_TRACE_DECL
 #define TFNO_TRACE_MARK()
 #define TFNO_TRACE_SINCE(slot)
+#define TFNO_TRACE_STEP(slot, expr) (expr)
 #define TFNO_TRACE_WAIT(slot, expr) (expr)
 #define TFNO_TRACE_FLUSH()
 #endif
@@ -126,10 +132,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when the barrier did not complete within the limit or another role
 // has already given up; the caller leaves its loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+// `idle_ns` > 0 marks a helper warp: it sleeps that long between polls from the first miss on, so
+// that its polling does not take issue slots from the compute warps of its scheduler partition.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          unsigned idle_ns = 0) {
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (spin > 64) {
+        if (idle_ns) {
+            __nanosleep(idle_ns);
+            if ((spin & 15) == 15 && *abort_flag) return false;
+        } else if (spin > 64) {
             if (*abort_flag) return false;
             __nanosleep(spin > 4096 ? 256 : 32);
         }
@@ -225,7 +237,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
     uint64_t* bars = reinterpret_cast<uint64_t*>(twI + R * 64);
     // barrier indices
     constexpr int B_FULL = 0, B_EMPTY = kStages, B_SFULL = 2 * kStages, B_SEMPTY = B_SFULL + 8, B_AFULL = B_SEMPTY + 8,
-                  B_AEMPTY = B_AFULL + 2, B_PFULL = B_AEMPTY + 2, B_PEMPTY = B_PFULL + 1, B_COUNT = B_PEMPTY + 1;
+                  B_AEMPTY = B_AFULL + 2, B_PFULL = B_AEMPTY + 2, B_PEMPTY = B_PFULL + 1, B_STAGGER = B_PEMPTY + 1, B_COUNT = B_STAGGER + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
@@ -246,6 +258,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
         for (int b = 0; b < 2; ++b) { mbar_init(bar(B_AFULL + b), 1); mbar_init(bar(B_AEMPTY + b), 4); }
         mbar_init(bar(B_PFULL), 4);
         mbar_init(bar(B_PEMPTY), 4);
+        mbar_init(bar(B_STAGGER), 2);
+        mbar_init(bar(B_STAGGER + 1), 2);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -308,8 +322,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
             bool ok = true;
             for (int it = 0; it < n_it && ok; ++it) {
                 const int buf = it & 1;
-                ok = TFNO_TRACE_WAIT(0, mbar_wait(bar(B_AFULL + buf), (it >> 1) & 1, abort_flag, p.status, 41));
-                if (ok) ok = TFNO_TRACE_WAIT(1, mbar_wait(bar(B_PEMPTY), (it & 1) ^ 1, abort_flag, p.status, 42));
+                ok = TFNO_TRACE_WAIT(0, mbar_wait(bar(B_AFULL + buf), (it >> 1) & 1, abort_flag, p.status, 41, kHelperIdleNs));
+                if (ok) ok = TFNO_TRACE_WAIT(1, mbar_wait(bar(B_PEMPTY), (it & 1) ^ 1, abort_flag, p.status, 42, kHelperIdleNs));
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
@@ -344,7 +358,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
             for (long long L = 0; L < n_loads && ok; ++L) {
                 const int s = (int)(L % kStages);
                 const uint32_t u = (uint32_t)(L / kStages);
-                ok = __all_sync(0xffffffffu, TFNO_TRACE_WAIT(0, mbar_wait(bar(B_EMPTY + s), (u & 1) ^ 1, abort_flag, p.status, 11)));
+                ok = __all_sync(0xffffffffu, TFNO_TRACE_WAIT(0, mbar_wait(bar(B_EMPTY + s), (u & 1) ^ 1, abort_flag, p.status, 11, kHelperIdleNs)));
                 if (!ok) break;
                 issue_load(L);
             }
@@ -357,8 +371,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 const int buf = it & 1;
                 const uint32_t d_tmem = tmem + TM_ACC + 64 * buf;
                 for (int c = 0; c < NC && ok; ++c) {
-                    ok = TFNO_TRACE_WAIT(0, mbar_wait(bar(B_SFULL + c), it & 1, abort_flag, p.status, 21));
-                    if (ok && c == 0) ok = TFNO_TRACE_WAIT(1, mbar_wait(bar(B_AEMPTY + buf), ((it >> 1) & 1) ^ 1, abort_flag, p.status, 22));
+                    ok = TFNO_TRACE_WAIT(0, mbar_wait(bar(B_SFULL + c), it & 1, abort_flag, p.status, 21, kHelperIdleNs));
+                    if (ok && c == 0) ok = TFNO_TRACE_WAIT(1, mbar_wait(bar(B_AEMPTY + buf), ((it >> 1) & 1) ^ 1, abort_flag, p.status, 22, kHelperIdleNs));
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll 1
@@ -381,16 +395,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;" ::: "memory");
     constexpr int GPW = 32 / R;                       // groups (channels) per warp
     const int g = lane % GPW, r = lane / GPW;         // lane = g + GPW*r: the R lanes of a group are GPW apart
-    const int half = (warp >> 1) & 1, wl = warp >> 2; // forward: half-team {0,4} / {2,6} and warp inside it
+    // forward: half-teams {0,2} and {4,6}: a scheduler partition (warps w and w+4) hosts one warp of
+    // each, and the second half-team starts half a task late, so that one warp's arithmetic
+    // overlaps the other's shuffles, shared-memory traffic and waits instead of colliding with it
+    const int half = (warp >> 2) & 1, wl = (warp >> 1) & 1;
+    bool stagger_pending = true;
     const int kl = wl * GPW + g;                      // forward: channel inside the chunk
     const int qi = warp >> 1;                         // inverse: 0..3
     constexpr int GROUPS = 128 / R;                   // inverse: channels per pass
     const int tasks_per_row = is_fwd ? (NC - half + 1) / 2 : 64 / GROUPS;
     bool alive = true;
 
+    TFNO_TRACE_MARK();
     for (int it = 0; it < n_it && alive; ++it) {
         const long long row = first + (long long)it * gridDim.x;
         for (int t = 0; t < tasks_per_row && alive; ++t) {
+            TFNO_TRACE_SINCE(10);
             float2 v[64];
             float sgn = 1.0f;
             int c = 0, n = 0, s = 0;
@@ -400,30 +420,27 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 const long long L = (long long)it * NC + c;
                 s = (int)(L % kStages);
                 const uint32_t u = (uint32_t)(L / kStages);
-                alive = __all_sync(0xffffffffu, TFNO_TRACE_WAIT(0, mbar_wait(bar(B_FULL + s), u & 1, abort_flag, p.status, 31)));
+                alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(0, mbar_wait(bar(B_FULL + s), u & 1, abort_flag, p.status, 31)));
                 if (!alive) break;
                 const float2* srow = reinterpret_cast<const float2*>(ring + s * G::STAGE_BYTES + kl * G::ROW_STRIDE);
-                TFNO_TRACE_MARK();
-#pragma unroll
+                #pragma unroll
                 for (int i = 0; i < 64; ++i) v[i] = srow[R * i + r];
                 TFNO_TRACE_SINCE(7);
                 sgn = (r & (R >> 1)) ? -1.0f : 1.0f;          // upper half of the group: spectrum rotated by 32
             } else {
                 if (t == 0) {
-                    alive = __all_sync(0xffffffffu, TFNO_TRACE_WAIT(0, mbar_wait(bar(B_PFULL), it & 1, abort_flag, p.status, 43)));
+                    alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(0, mbar_wait(bar(B_PFULL), it & 1, abort_flag, p.status, 43)));
                     if (!alive) break;
                 }
-                TFNO_TRACE_MARK();
-                n = t * GROUPS + qi * GPW + g;
+                                n = t * GROUPS + qi * GPW + g;
                 const float* pre = planes + n * 64;
                 const float* pim = planes + 4096 + n * 64;
-                const float2* tw = twI + 64 * r;
 #pragma unroll
                 for (int cc = 0; cc < 16; ++cc) {
                     const float4 a = *reinterpret_cast<const float4*>(pre + plane_chunk(n, cc) * 4);
                     const float4 b = *reinterpret_cast<const float4*>(pim + plane_chunk(n, cc) * 4);
-                    const float4 t0 = *reinterpret_cast<const float4*>(tw + 4 * cc);
-                    const float4 t1 = *reinterpret_cast<const float4*>(tw + 4 * cc + 2);
+                    const float4 t0 = *reinterpret_cast<const float4*>(twI + tw_index<R>(r, 4 * cc));
+                    const float4 t1 = *reinterpret_cast<const float4*>(twI + tw_index<R>(r, 4 * cc + 2));
                     const float2 u0 = cmul(make_float2(a.x, b.x), make_float2(t0.x, t0.y));
                     const float2 u1 = cmul(make_float2(a.y, b.y), make_float2(t0.z, t0.w));
                     const float2 u2 = cmul(make_float2(a.z, b.z), make_float2(t1.x, t1.y));
@@ -438,32 +455,39 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
             }
 
             // ------------------------------ the one 64-point transform ------------------------------
-            TFNO_TRACE_WAIT(6, (fft64<-1>(v, sgn), true));
+            if (stagger_pending && (warp >> 2) == 1) {
+                // once: warps 4-7 wait until their partition mates have finished a first transform
+                alive = __all_sync(0xffffffffu, mbar_wait(bar(B_STAGGER + (is_fwd ? 0 : 1)), 0, abort_flag, p.status, 51));
+                if (!alive) break;
+            }
+            fft64<-1>(v, sgn);
+            TFNO_TRACE_SINCE(6);
+            if (stagger_pending && (warp >> 2) == 0) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_STAGGER + (is_fwd ? 0 : 1)));
+            }
+            stagger_pending = false;
 
             // ------------------------------ epilogue ------------------------------
             if (is_fwd) {
                 // every input sample has been consumed by now: hand the ring stage back
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_EMPTY + s));
-                const float2* tw = twF + 64 * r;
-                TFNO_TRACE_MARK();
-#pragma unroll
+                #pragma unroll
                 for (int j = 0; j < 64; j += 2) {
-                    const float4 tt = *reinterpret_cast<const float4*>(tw + j);
+                    const float4 tt = *reinterpret_cast<const float4*>(twF + tw_index<R>(r, j));
                     v[slot(j)] = cmul(v[slot(j)], make_float2(tt.x, tt.y));
                     v[slot(j + 1)] = cmul(v[slot(j + 1)], make_float2(tt.z, tt.w));
                 }
                 // reduce-scatter over the R lanes of the group (GPW apart)
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[slot(j)] = cadd(v[slot(j)], shfl_xor2(v[slot(32 + j)], (R >> 1) * GPW));
+                exchange_round_top(v, (R >> 1) * GPW);
                 if constexpr (R >= 4) exchange_round<16>(v, (R >> 2) * GPW, (r & (R >> 2)) != 0);
                 // lane r now holds modes 64/R*r + j, j < 64/R, in v[slot(j)]
                 TFNO_TRACE_SINCE(8);
-                alive = __all_sync(0xffffffffu, TFNO_TRACE_WAIT(1, mbar_wait(bar(B_SEMPTY + c), (it & 1) ^ 1, abort_flag, p.status, 32)));
+                alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(1, mbar_wait(bar(B_SEMPTY + c), (it & 1) ^ 1, abort_flag, p.status, 32)));
                 if (!alive) break;
                 constexpr int PER = 64 / R;
-                TFNO_TRACE_MARK();
-                const int kk_re = c * 2 * CH + kl, kk_im = kk_re + CH;
+                                const int kk_re = c * 2 * CH + kl, kk_im = kk_re + CH;
                 unsigned char* hi_re = sS + (kk_re >> 2) * kLBO + (kk_re & 3) * 4;
                 unsigned char* hi_im = sS + (kk_im >> 2) * kLBO + (kk_im & 3) * 4;
 #pragma unroll
@@ -488,8 +512,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                     if (lane == 0) mbar_arrive(bar(B_PEMPTY));
                 }
                 float2* dst = p.y + row * p.y_stride_row + (long long)n * p.y_stride_n;
-                TFNO_TRACE_MARK();
-#pragma unroll
+                #pragma unroll
                 for (int j2 = 0; j2 < 64; ++j2) {
                     const float2 o = v[slot(j2)];
                     dst[R * j2 + r] = INVERSE ? make_float2(o.y, o.x) : o;
