@@ -50,7 +50,8 @@ def hbm_peak():
 
 
 def traffic_per_row():
-    """DRAM bytes per signal row of the fused kernel from the committed ncu capture, if any."""
+    """DRAM bytes (read + write) per signal row of the fused kernel, from the committed ncu
+    capture (profiles/traffic.json); traffic grows in proportion to the rows a launch processes."""
     p = os.path.join(ROOT, "profiles", "traffic.json")
     try:
         with open(p) as f:
@@ -60,22 +61,57 @@ def traffic_per_row():
 
 
 class ClockSampler:
+    """Samples SM clock and clock-event (throttle) reasons of one GPU while the timed region runs:
+    through NVML every few milliseconds, or, if NVML cannot be loaded, by calling nvidia-smi."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index):
         self.index, self.samples, self._stop = index, [], threading.Event()
         self._t = threading.Thread(target=self._run, daemon=True)
+        self._nvml = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index(index))
+            self._max = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    @staticmethod
+    def _physical_index(index):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if index < len(ids) and ids[index].isdigit():
+                return int(ids[index])
+        return index
+
+    def _sample_nvml(self):
+        n = self._nvml
+        mhz = n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM)
+        try:
+            bits = n.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+        except Exception:
+            bits = n.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+        flags = [bool(bits & 0x8), bool(bits & 0x40), bool(bits & 0x20), bool(bits & 0x4)]   # hw_slowdown, hw_thermal, sw_thermal, sw_power_cap
+        self.samples.append([str(mhz), str(self._max)] + ["Active" if f else "Not Active" for f in flags])
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.check_output(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
-                                               "--format=csv,noheader,nounits"], text=True, timeout=5)
-                self.samples.append([s.strip() for s in out.strip().split(",")])
+                if self._nvml is not None:
+                    self._sample_nvml()
+                else:
+                    out = subprocess.check_output(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
+                                                   "--format=csv,noheader,nounits"], text=True, timeout=5)
+                    self.samples.append([x.strip() for x in out.strip().split(",")])
             except Exception:
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(0.002 if self._nvml is not None else 0.2)
 
     def __enter__(self):
         self._t.start()
@@ -86,13 +122,13 @@ class ClockSampler:
         self._t.join(timeout=6)
 
     def summary(self):
-        sm = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
+        sm = sorted(int(x[0]) for x in self.samples if x and x[0].isdigit())
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(s) > 2 + i and s[2 + i].lower().startswith("active") for s in self.samples)]
-        smax = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(smax) if smax else None, "reasons": reasons, "samples": len(sm)}
+        reasons = [n for i, n in enumerate(self.NAMES) if any(len(x) > 2 + i and x[2 + i].lower().startswith("active") for x in self.samples)]
+        smax = [int(x[1]) for x in self.samples if len(x) > 1 and x[1].isdigit()]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": max(smax) if smax else None, "reasons": reasons,
+                "samples": len(sm), "source": "nvml" if self._nvml is not None else "nvidia-smi"}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -161,6 +197,51 @@ def time_reference_gpu_variant_e(w):
     except Exception:
         return None
     return None
+
+
+def time_2d_configs(t, dev):
+    """Not bench lines: the 2D parity configurations of BASELINE.json timed once for context
+    (variant D = image FFT, CGEMM, image iFFT; variant E = cuFFT + cuBLAS)."""
+    import torch
+
+    out = {}
+    for name, bs, K, N, D, layers in (("config2_2d_bs16_k32_n64_256x256", 16, 32, 64, 256, 1),
+                                      ("config4_2d_bs256_k64_n64_256x256_4_layers", 256, 64, 64, 256, 4)):
+        try:
+            g = torch.Generator(device=dev).manual_seed(7)
+            a = torch.empty((K, bs, D, D), dtype=torch.complex64, device=dev)
+            for k in range(K):
+                a[k] = torch.view_as_complex(torch.rand((bs, D, D, 2), device=dev, generator=g) * 2 - 1)
+            b = torch.empty((N, bs, D, D), dtype=torch.complex64, device=dev)
+            ws = [torch.view_as_complex(torch.randn((N, K, 2), device=dev, generator=g) / (K ** 0.5)) for _ in range(layers)]
+            res = {}
+            for variant in ("D", "E"):
+                plan = t.SpectralConv(2, bs, D, K, N, DX=D, variant=variant)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 3
+                for it in range(reps + 1):
+                    if it == 1:
+                        e0.record()
+                    src, dst = a, b
+                    for l in range(layers):
+                        plan(src, ws[l], y=dst)
+                        if K == N:
+                            src, dst = dst, src
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / reps / layers
+                bytes_layer = 8 * bs * D * D * (K + N)
+                res[variant] = {"ms_per_layer": ms, "algorithmic_GBps": bytes_layer / ms * 1e-6}
+                plan.close()
+                del plan
+            peak, _ = hbm_peak()
+            res["D_frac_of_hbm_peak"] = res["D"]["algorithmic_GBps"] / peak
+            out[name] = res
+            del a, b
+            torch.cuda.empty_cache()
+        except Exception as e:      # context only: never fail the bench line over it
+            out[name] = {"error": str(e)[:200]}
+    return out
 
 
 def run_gpu_arm(args, rank, world, local_rank):
@@ -249,7 +330,7 @@ def run_gpu_arm(args, rank, world, local_rank):
             "aggregate_algorithmic_GBps": algorithmic_bytes(w["bs"], w["dimX"], DY, K, N) / (ms_per_step * 1e-3) / 1e9,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": (tr * rows_local) if tr else None, "peak_source": peak_src,
-                         "kernel": "spectral_tile_kernel<4,true,true,1>", "algorithmic_bytes_per_launch": step_bytes},
+                         "kernel": "tfno::tc::spectral_tc_kernel<4,true> (tcgen05 fused FFT+CGEMM+iFFT)", "algorithmic_bytes_per_launch": step_bytes},
             "e2e": {"value": 1000.0 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 8 * (w["bs"] * w["dimX"] * DY * K + K * N * world),
                     "d2h_bytes_per_step": 8 * w["bs"] * w["dimX"] * DY * N, "max_abs_diff_vs_device_path": e2e_check},
@@ -273,6 +354,10 @@ def run_gpu_arm(args, rank, world, local_rank):
             torch.cuda.synchronize()
             line["variant_E_stream_ordered_ms"] = ev0.elapsed_time(ev1) / 10
             pe.close()
+            del xs, ys
+            torch.cuda.empty_cache()
+            if not args.no_extras:
+                line["extras"] = time_2d_configs(t, dev)
         print(json.dumps(line), flush=True)
     plan.close()
     if dist is not None:
@@ -286,6 +371,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the 2D context timings (N=1 only)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
