@@ -42,7 +42,7 @@ namespace tfno {
 namespace tc {
 
 constexpr int kTcThreads = 512;               // 4 warpgroups, see the role table above
-constexpr int kStages = 3;
+constexpr int kStages = 2;                  // ring stages: one in flight per forward half-team
 constexpr int kLBO = 144;                   // bytes between K-adjacent core matrices of S (128 + 16 pad)
 constexpr uint32_t kSpinLimit = 1u << 22;   // polls (with back-off) before a wait gives up
 #ifndef TFNO_HELPER_IDLE_NS
@@ -78,16 +78,16 @@ struct TcParams {
     long long* trace;           // optional per-warp cycle counters (builds with TFNO_TC_TRACE only)
 };
 
+// S holds ONE chunk (CH channels) per buffer; there are two buffers, one per forward half-team.
 // SBO: bytes between 8-mode groups of S.  The R lanes of a group store modes 64/R apart in the
-// same instruction, i.e. 8/R groups apart: SBO is the span of all K chunks rounded up so that
+// same instruction, i.e. 8/R groups apart: SBO is the span of the chunk's K columns rounded up so that
 // (8/R)*SBO is 32 bytes (R = 4) or 64 bytes (R = 2) past a multiple of 128 -- both hold when SBO
 // is 16 past a multiple of 64 -- and the lanes of a warp fall into 32 different banks.
-__host__ __device__ inline int s_sbo(int K, int R) {
-    const int span = (2 * K / 4) * kLBO;
-    (void)R;
+__host__ __device__ inline int s_sbo(int R) {
+    const int span = (2 * (64 / R) / 4) * kLBO;           // one chunk: CH channels, Re and Im rows
     return ((span + 63) / 64) * 64 + 16;
 }
-__host__ __device__ inline int s_bytes(int K, int R) { return 8 * s_sbo(K, R); }   // one of the hi / lo arrays
+__host__ __device__ inline int s_bytes(int R) { return 8 * s_sbo(R); }   // the hi or the lo array of one chunk buffer
 
 template <int R> struct Geometry {
     static constexpr int DY = 64 * R;
@@ -96,6 +96,12 @@ template <int R> struct Geometry {
     static constexpr int ROW_STRIDE = ROW_BYTES + 16;       // pad: 8 rows x 16 B tile the 128-byte bank window
     static constexpr int STAGE_BYTES = CH * ROW_STRIDE;
     static constexpr int KSTEPS_PER_CHUNK = 2 * CH / 8;
+    // Output rows are staged in shared memory and leave through the bulk-copy engine when there is
+    // room (DY = 256); at DY = 128 the S buffers are twice as large and the lanes store directly.
+    static constexpr bool STAGED_OUT = (R == 4);
+    static constexpr int OUT_ROWS = 32 / R;                 // output rows staged per inverse warp and task
+    static constexpr int OUT_STRIDE = ROW_BYTES + 16;       // padded like the input rows
+    static constexpr int OUT_BYTES = STAGED_OUT ? OUT_ROWS * OUT_STRIDE : 0;   // per inverse warp
 };
 
 template <int R>
@@ -103,7 +109,9 @@ __host__ inline size_t tc_smem_bytes(int K) {
     using G = Geometry<R>;
     size_t b = 0;
     b += (size_t)kStages * G::STAGE_BYTES;        // ring
-    b += 2 * (size_t)s_bytes(K, R);               // S hi, S lo
+    (void)K;
+    b += 2 * 2 * (size_t)s_bytes(R);              // two chunk buffers of S, hi and lo each
+    b += 4 * (size_t)G::OUT_BYTES;                // output staging, one per inverse warp
     b += 2 * 64 * 256;                            // Re / Im planes [64 channels][64 modes] fp32
     b += 2 * (size_t)R * 64 * 8;                  // twiddle tables
     b += 256;                                     // barriers, tmem base, abort flag
@@ -228,11 +236,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int K = p.K;
     const int NC = K / CH;                            // chunks per row
-    const int SBO = s_sbo(K, R), SBYTES = s_bytes(K, R);
+    const int SBO = s_sbo(R), SBYTES = s_bytes(R);
     unsigned char* ring = base;
-    unsigned char* sS = ring + kStages * G::STAGE_BYTES;            // [hi | lo]
-    float* planes = reinterpret_cast<float*>(sS + 2 * SBYTES);      // [2][64][64]
-    float2* twF = reinterpret_cast<float2*>(planes + 2 * 64 * 64);
+    unsigned char* sS = ring + kStages * G::STAGE_BYTES;            // [buffer 0: hi | lo][buffer 1: hi | lo]
+    float* planes = reinterpret_cast<float*>(sS + 4 * SBYTES);      // [2][64][64]
+    unsigned char* ostage = reinterpret_cast<unsigned char*>(planes + 2 * 64 * 64);   // [4 warps][OUT_ROWS][OUT_STRIDE]
+    float2* twF = reinterpret_cast<float2*>(ostage + 4 * G::OUT_BYTES);
     float2* twI = twF + R * 64;
     uint64_t* bars = reinterpret_cast<uint64_t*>(twI + R * 64);
     // barrier indices
@@ -254,7 +263,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
     // ---------------- set-up ----------------
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 2); }
-        for (int c = 0; c < 8; ++c) { mbar_init(bar(B_SFULL + c), 2); mbar_init(bar(B_SEMPTY + c), 1); }
+        for (int c = 0; c < 2; ++c) { mbar_init(bar(B_SFULL + c), 2); mbar_init(bar(B_SEMPTY + c), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar(B_AFULL + b), 1); mbar_init(bar(B_AEMPTY + b), 4); }
         mbar_init(bar(B_PFULL), 4);
         mbar_init(bar(B_PEMPTY), 4);
@@ -365,27 +374,30 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
         } else if (warp == 13 && lane == 0) {
             // MMA issuer
             const uint32_t idesc = make_idesc_tf32(64);
-            const uint32_t s_hi = smem_u32(sS), s_lo = s_hi + SBYTES;
             bool ok = true;
             for (int it = 0; it < n_it && ok; ++it) {
                 const int buf = it & 1;
                 const uint32_t d_tmem = tmem + TM_ACC + 64 * buf;
                 for (int c = 0; c < NC && ok; ++c) {
-                    ok = TFNO_TRACE_WAIT(0, mbar_wait(bar(B_SFULL + c), it & 1, abort_flag, p.status, 21, kHelperIdleNs));
+                    // chunk c sits in S buffer h = c & 1; it is the j-th chunk its half-team has produced
+                    const int h = c & 1;
+                    const uint32_t j = (uint32_t)it * (uint32_t)((NC - h + 1) / 2) + (uint32_t)(c >> 1);
+                    ok = TFNO_TRACE_WAIT(0, mbar_wait(bar(B_SFULL + h), j & 1, abort_flag, p.status, 21, kHelperIdleNs));
                     if (ok && c == 0) ok = TFNO_TRACE_WAIT(1, mbar_wait(bar(B_AEMPTY + buf), ((it >> 1) & 1) ^ 1, abort_flag, p.status, 22, kHelperIdleNs));
                     if (!ok) break;
                     tc_fence_after();
+                    const uint32_t s_hi = smem_u32(sS) + (uint32_t)(2 * h * SBYTES), s_lo = s_hi + SBYTES;
 #pragma unroll 1
-                    for (int j = 0; j < G::KSTEPS_PER_CHUNK; ++j) {
-                        const int ks = c * G::KSTEPS_PER_CHUNK + j;               // k-step: kk in [8ks, 8ks+8)
-                        const uint64_t dhi = make_kmajor_desc(s_hi + 2 * ks * kLBO, kLBO, SBO);
-                        const uint64_t dlo = make_kmajor_desc(s_lo + 2 * ks * kLBO, kLBO, SBO);
+                    for (int jj = 0; jj < G::KSTEPS_PER_CHUNK; ++jj) {
+                        const int ks = c * G::KSTEPS_PER_CHUNK + jj;              // k-step of the row: kk in [8ks, 8ks+8)
+                        const uint64_t dhi = make_kmajor_desc(s_hi + 2 * jj * kLBO, kLBO, SBO);
+                        const uint64_t dlo = make_kmajor_desc(s_lo + 2 * jj * kLBO, kLBO, SBO);
                         const uint32_t a_hi = tmem + TM_WHI + 8 * ks, a_lo = tmem + TM_WLO + 8 * ks;
-                        umma_tf32_ts(d_tmem, a_hi, dhi, idesc, (c | j) ? 1u : 0u);
+                        umma_tf32_ts(d_tmem, a_hi, dhi, idesc, (c | jj) ? 1u : 0u);
                         umma_tf32_ts(d_tmem, a_lo, dhi, idesc, 1u);
                         umma_tf32_ts(d_tmem, a_hi, dlo, idesc, 1u);
                     }
-                    umma_commit(bar(B_SEMPTY + c));
+                    umma_commit(bar(B_SEMPTY + h));
                     if (c == NC - 1) umma_commit(bar(B_AFULL + buf));
                 }
             }
@@ -423,7 +435,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(0, mbar_wait(bar(B_FULL + s), u & 1, abort_flag, p.status, 31)));
                 if (!alive) break;
                 const float2* srow = reinterpret_cast<const float2*>(ring + s * G::STAGE_BYTES + kl * G::ROW_STRIDE);
-                #pragma unroll
+#pragma unroll
                 for (int i = 0; i < 64; ++i) v[i] = srow[R * i + r];
                 TFNO_TRACE_SINCE(7);
                 sgn = (r & (R >> 1)) ? -1.0f : 1.0f;          // upper half of the group: spectrum rotated by 32
@@ -432,7 +444,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                     alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(0, mbar_wait(bar(B_PFULL), it & 1, abort_flag, p.status, 43)));
                     if (!alive) break;
                 }
-                                n = t * GROUPS + qi * GPW + g;
+                n = t * GROUPS + qi * GPW + g;
                 const float* pre = planes + n * 64;
                 const float* pim = planes + 4096 + n * 64;
 #pragma unroll
@@ -473,7 +485,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 // every input sample has been consumed by now: hand the ring stage back
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_EMPTY + s));
-                #pragma unroll
+#pragma unroll
                 for (int j = 0; j < 64; j += 2) {
                     const float4 tt = *reinterpret_cast<const float4*>(twF + tw_index<R>(r, j));
                     v[slot(j)] = cmul(v[slot(j)], make_float2(tt.x, tt.y));
@@ -484,12 +496,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 if constexpr (R >= 4) exchange_round<16>(v, (R >> 2) * GPW, (r & (R >> 2)) != 0);
                 // lane r now holds modes 64/R*r + j, j < 64/R, in v[slot(j)]
                 TFNO_TRACE_SINCE(8);
-                alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(1, mbar_wait(bar(B_SEMPTY + c), (it & 1) ^ 1, abort_flag, p.status, 32)));
+                // this half-team's S buffer is free once the MMAs of its previous chunk have completed
+                const uint32_t jchunk = (uint32_t)it * (uint32_t)tasks_per_row + (uint32_t)t;
+                alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(1, mbar_wait(bar(B_SEMPTY + half), (jchunk & 1) ^ 1, abort_flag, p.status, 32)));
                 if (!alive) break;
                 constexpr int PER = 64 / R;
-                                const int kk_re = c * 2 * CH + kl, kk_im = kk_re + CH;
-                unsigned char* hi_re = sS + (kk_re >> 2) * kLBO + (kk_re & 3) * 4;
-                unsigned char* hi_im = sS + (kk_im >> 2) * kLBO + (kk_im & 3) * 4;
+                const int kk_re = kl, kk_im = CH + kl;                 // K row inside the chunk buffer
+                unsigned char* sbuf = sS + 2 * half * SBYTES;
+                unsigned char* hi_re = sbuf + (kk_re >> 2) * kLBO + (kk_re & 3) * 4;
+                unsigned char* hi_im = sbuf + (kk_im >> 2) * kLBO + (kk_im & 3) * 4;
 #pragma unroll
                 for (int j = 0; j < PER; ++j) {
                     const int m = PER * r + j;
@@ -503,7 +518,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 }
                 fence_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_SFULL + c));
+                if (lane == 0) mbar_arrive(bar(B_SFULL + half));
                 TFNO_TRACE_SINCE(9);
             } else {
                 if (t == tasks_per_row - 1) {
@@ -511,16 +526,42 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar(B_PEMPTY));
                 }
-                float2* dst = p.y + row * p.y_stride_row + (long long)n * p.y_stride_n;
-                #pragma unroll
+                // Stage the warp's OUT_ROWS output rows in shared memory and hand each row to the
+                // bulk-copy engine: the rows leave as full lines instead of 32-byte pieces through
+                // the load/store unit.  The lanes that issue the copies first wait until their
+                // previous copies have finished reading the staging buffer.
+                if constexpr (!G::STAGED_OUT) {
+                    float2* dst = p.y + row * p.y_stride_row + (long long)n * p.y_stride_n;
+#pragma unroll
+                    for (int j2 = 0; j2 < 64; ++j2) {
+                        const float2 o = v[slot(j2)];
+                        dst[R * j2 + r] = INVERSE ? make_float2(o.y, o.x) : o;
+                    }
+                } else {
+                unsigned char* ost = ostage + qi * G::OUT_BYTES;
+                if (lane < G::OUT_ROWS) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                __syncwarp();
+                float2* srow_out = reinterpret_cast<float2*>(ost + g * G::OUT_STRIDE);
+#pragma unroll
                 for (int j2 = 0; j2 < 64; ++j2) {
                     const float2 o = v[slot(j2)];
-                    dst[R * j2 + r] = INVERSE ? make_float2(o.y, o.x) : o;
+                    srow_out[R * j2 + r] = INVERSE ? make_float2(o.y, o.x) : o;
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane < G::OUT_ROWS) {
+                    const int nn = t * GROUPS + qi * GPW + lane;
+                    float2* dst = p.y + row * p.y_stride_row + (long long)nn * p.y_stride_n;
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                 ::"l"(dst), "r"(smem_u32(ost + lane * G::OUT_STRIDE)), "r"(G::ROW_BYTES) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
                 }
                 TFNO_TRACE_SINCE(9);
             }
         }
     }
+    if (is_inv) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all output rows have landed
     }   // forward / inverse warps
 
     // ---------------- teardown ----------------
