@@ -139,24 +139,29 @@ def time_cpu_port(steps, warmup, budget_s=20.0):
     from oracle import oracle_c
 
     w = WORKLOAD
-    threads = oracle_c.max_threads()
+    # all host threads this process may use (torchrun exports OMP_NUM_THREADS=1, which would
+    # otherwise turn the CPU arm into a single-thread run)
+    try:
+        threads = len(os.sched_getaffinity(0))
+    except AttributeError:
+        threads = os.cpu_count() or 1
     rng = np.random.default_rng(1234)
     probe = 128
     xs = (rng.uniform(-1, 1, (probe, w["K"], w["DY"])) + 1j * rng.uniform(-1, 1, (probe, w["K"], w["DY"]))).astype(np.complex64)
     ws = ((rng.standard_normal((w["K"], w["N"])) + 1j * rng.standard_normal((w["K"], w["N"]))) / np.sqrt(w["K"])).astype(np.complex64)
-    oracle_c.spectral_conv_1d(xs, ws, double=False)                   # load + first touch
+    oracle_c.spectral_conv_1d(xs, ws, double=False, threads=threads)  # load + first touch
     t0 = time.perf_counter()
-    oracle_c.spectral_conv_1d(xs, ws, double=False)
+    oracle_c.spectral_conv_1d(xs, ws, double=False, threads=threads)
     per_row = (time.perf_counter() - t0) / probe
     total_iters = max(1, steps + warmup)
     rows = int(max(probe, min(w["bs"], budget_s / total_iters / max(per_row, 1e-9))))
     rows -= rows % 64 if rows >= 64 else 0
     x = (rng.uniform(-1, 1, (rows, w["K"], w["DY"])) + 1j * rng.uniform(-1, 1, (rows, w["K"], w["DY"]))).astype(np.complex64)
     for _ in range(warmup):
-        oracle_c.spectral_conv_1d(x, ws, double=False)
+        oracle_c.spectral_conv_1d(x, ws, double=False, threads=threads)
     t0 = time.perf_counter()
     for _ in range(steps):
-        oracle_c.spectral_conv_1d(x, ws, double=False)
+        oracle_c.spectral_conv_1d(x, ws, double=False, threads=threads)
     dt = (time.perf_counter() - t0) / max(steps, 1)
     layers_per_s = (rows / w["bs"]) / dt
     sample = "%d of %d signal rows per step (float32 C port of the path, OpenMP), scaled linearly to the full batch" % (rows, w["bs"])

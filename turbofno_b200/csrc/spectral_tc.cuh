@@ -437,6 +437,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 const float2* srow = reinterpret_cast<const float2*>(ring + s * G::STAGE_BYTES + kl * G::ROW_STRIDE);
 #pragma unroll
                 for (int i = 0; i < 64; ++i) v[i] = srow[R * i + r];
+                // Hand the stage back for the next asynchronous (bulk-copy) overwrite.  The fence
+                // waits until this thread's loads have returned: __syncwarp alone does not, and a
+                // stage released with loads still in flight was overwritten under them.
+                __threadfence_block();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_EMPTY + s));
                 TFNO_TRACE_SINCE(7);
                 sgn = (r & (R >> 1)) ? -1.0f : 1.0f;          // upper half of the group: spectrum rotated by 32
             } else {
@@ -482,9 +488,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
 
             // ------------------------------ epilogue ------------------------------
             if (is_fwd) {
-                // every input sample has been consumed by now: hand the ring stage back
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_EMPTY + s));
 #pragma unroll
                 for (int j = 0; j < 64; j += 2) {
                     const float4 tt = *reinterpret_cast<const float4*>(twF + tw_index<R>(r, j));
@@ -541,12 +544,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 unsigned char* ost = ostage + qi * G::OUT_BYTES;
                 if (lane < G::OUT_ROWS) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 __syncwarp();
+                TFNO_TRACE_SINCE(2);
                 float2* srow_out = reinterpret_cast<float2*>(ost + g * G::OUT_STRIDE);
 #pragma unroll
                 for (int j2 = 0; j2 < 64; ++j2) {
                     const float2 o = v[slot(j2)];
                     srow_out[R * j2 + r] = INVERSE ? make_float2(o.y, o.x) : o;
                 }
+                TFNO_TRACE_SINCE(3);
                 fence_async_smem();
                 __syncwarp();
                 if (lane < G::OUT_ROWS) {
