@@ -45,6 +45,7 @@ constexpr int kTcThreads = 512;               // 4 warpgroups, see the role tabl
 constexpr int kStages = 2;                  // ring stages: one in flight per forward half-team
 constexpr int kLBO = 144;                   // bytes between K-adjacent core matrices of S (128 + 16 pad)
 constexpr uint32_t kSpinLimit = 1u << 22;   // polls (with back-off) before a wait gives up
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;   // and wall-clock limit of one wait: 1 s
 #ifndef TFNO_HELPER_IDLE_NS
 #define TFNO_HELPER_IDLE_NS 200
 #endif
@@ -144,8 +145,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // that its polling does not take issue slots from the compute warps of its scheduler partition.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
                                           unsigned idle_ns = 0) {
+    unsigned long long t0 = 0;
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 1023) == 1023) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) break;
+        }
         if (idle_ns) {
             __nanosleep(idle_ns);
             if ((spin & 15) == 15 && *abort_flag) return false;
@@ -155,7 +163,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
     *abort_flag = 1;
-    atomicCAS(status, 0, code);
+    if (status) atomicCAS(status, 0, code);
     return false;
 }
 __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
