@@ -403,6 +403,12 @@ struct ImageParams {
 
 // [image][DX][DY] -> [image][64][64]: Y transform of every row (kept modes only) into shared
 // memory, then X transform of the 64 kept columns.
+// Ask the L2 for `bytes` of contiguous global memory, one 128-byte line per thread and round.
+__device__ __forceinline__ void prefetch_l2_block(const void* base, int bytes, int tid, int nthreads) {
+    const char* b = static_cast<const char*>(base);
+    for (int off = tid * 128; off < bytes; off += nthreads * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(b + off));
+}
+
 template <int RX, int RY>
 __global__ void __launch_bounds__(kThreads, 1) fft2d_trunc_kernel(ImageParams p) {
     constexpr int DX = 64 * RX, DY = 64 * RY;
@@ -424,6 +430,15 @@ __global__ void __launch_bounds__(kThreads, 1) fft2d_trunc_kernel(ImageParams p)
                 const int x = x0 + g;
                 float2 v[64];
                 load_decimated<RY>(v, src + (long long)x * DY, 1, r);
+                // While these rows are transformed, the rows of the next round (or the first rows
+                // of this CTA's next image) travel from DRAM to the L2: a warp has no other loads
+                // in flight while it computes, and only two warps share a scheduler.
+                if (x0 + GROUPS < DX) {
+                    prefetch_l2_block(src + (long long)(x0 + GROUPS) * DY, GROUPS * DY * 8, tid, kThreads);
+                } else if (img + gridDim.x < p.nimg) {
+                    const long long nx = img + gridDim.x;
+                    prefetch_l2_block(p.in + (nx % p.per_k) * p.stride_b + (nx / p.per_k) * p.stride_k, GROUPS * DY * 8, tid, kThreads);
+                }
                 forward_trunc<RY>(v, twY, r);
                 store_modes_to_tile<RY>(v, sY, x, r);
             }
