@@ -64,6 +64,34 @@ def test_cgemm(cuda, rows, K, N):
     assert_close(C.cpu().numpy(), ref, "cgemm")
 
 
+@pytest.mark.parametrize("rows,K", [(1, 16), (7, 32), (149, 48), (600, 64), (296, 16), (1000, 48)])
+def test_cgemm_beta_zero_takes_the_tensor_core_kernel(cuda, rows, K):
+    """beta = 0, N = 64, K a multiple of 16: the contraction runs on tcgen05 (cgemm_tc_kernel), every
+    other case on the FP32 kernel; both must agree with the float64 product. Even row counts of at
+    least two per SM use 128-mode tiles, the others 64-mode tiles. 149 and 600 tiles give
+    the CTAs of a 148-SM device one, two and five tiles (double-buffered accumulators, both ring
+    stages of a half-team); C starts as NaN to show that every element is written."""
+    import torch
+    import turbofno_b200 as t
+
+    N, M = 64, rows * 64
+    rng = np.random.default_rng(100 * rows + K)
+    A = (rng.uniform(-1, 1, (K, M)) + 1j * rng.uniform(-1, 1, (K, M))).astype(np.complex64)
+    Bm = ((rng.standard_normal((N, K)) + 1j * rng.standard_normal((N, K))) / np.sqrt(K)).astype(np.complex64)
+    alpha = 0.75 - 0.5j
+    C = torch.full((N, M), float("nan"), dtype=torch.complex64, device=cuda)
+    t.cgemm(M, N, K, _dev(cuda, A), _dev(cuda, Bm), C, alpha, 0.0)
+    ref = alpha * (Bm.astype(np.complex128) @ A.astype(np.complex128))
+    got = C.cpu().numpy()
+    assert np.isfinite(got.view(np.float32)).all()
+    assert_close(got, ref, "cgemm (tensor cores)")
+    assert t.Handle.get(0).device_status == 0
+    # same inputs with a non-zero beta (FP32 kernel) differ from it by rounding only
+    C2 = torch.zeros((N, M), dtype=torch.complex64, device=cuda)
+    t.cgemm(M, N, K, _dev(cuda, A), _dev(cuda, Bm), C2, alpha, 1.0)
+    assert_close(C2.cpu().numpy(), ref, "cgemm (FP32 kernel)")
+
+
 @pytest.mark.parametrize("DY", [128, 256])
 def test_partial_fusions(cuda, DY):
     import torch

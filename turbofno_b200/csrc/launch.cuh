@@ -6,6 +6,7 @@
 #include "../../include/turbofno_b200.h"
 #include "spectral_kernels.cuh"
 #include "spectral_tc.cuh"
+#include "cgemm_tc.cuh"
 
 namespace tfno {
 
@@ -123,6 +124,40 @@ inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream
     return launch_status();
 }
 
+// Tensor-core contraction of compact spectra: N = 64, K a multiple of 16 up to 64, beta = 0.
+inline bool cgemm_tc_eligible(const DeviceInfo& dev, const TileParams& p) {
+    if (!dev.use_tensor_cores || !dev.status) return false;
+    if (p.N != 64 || p.K < tcg::kCH || p.K > 64 || p.K % tcg::kCH != 0) return false;
+    if (p.beta.x != 0.f || p.beta.y != 0.f) return false;
+    return ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.y)) & 15) == 0;
+}
+template <int TN>
+inline int launch_cgemm_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
+    auto kernel = tcg::cgemm_tc_kernel<TN>;
+    const size_t smem = tcg::cgemm_tc_smem_bytes<TN>();
+    if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return TFNO_ERR_CUDA;
+    }
+    const long long M = p.rows * kModes;
+    tcg::CgemmTcParams q{};
+    q.tiles = M / TN; q.K = p.K;
+    q.a = p.x; q.a_stride_k = M;
+    q.w = p.w; q.w_stride_k = p.w_stride_k; q.w_stride_n = p.w_stride_n;
+    q.c = p.y; q.c_stride_n = M;
+    q.alpha = p.alpha; q.status = dev.status;
+    long long grid = dev.sms;
+    if (grid > q.tiles) grid = q.tiles;
+    kernel<<<(unsigned)grid, tcg::kGemmThreads, smem, st>>>(q);
+    return launch_status();
+}
+// 128-mode tiles when M allows it and there are enough of them to fill the device
+inline int launch_cgemm_tc(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
+    if (p.rows % 2 == 0 && p.rows / 2 >= dev.sms) return launch_cgemm_tc_inst<128>(dev, p, st);
+    return launch_cgemm_tc_inst<64>(dev, p, st);
+}
+
 // Row-tile kernel for any N that is a multiple of 64: output channels are processed in blocks of
 // at most 128 (one launch per block; N <= 128, the whole reference grid, is a single launch).
 template <bool FWD, bool INV>
@@ -136,6 +171,9 @@ inline int launch_tile(const DeviceInfo& dev, int len, TileParams p, cudaStream_
             if (p.conj_inverse) return len == 128 ? launch_tc_inst<2, true>(dev, p, st) : launch_tc_inst<4, true>(dev, p, st);
             return len == 128 ? launch_tc_inst<2, false>(dev, p, st) : launch_tc_inst<4, false>(dev, p, st);
         }
+    }
+    if constexpr (!FWD && !INV) {
+        if (cgemm_tc_eligible(dev, p)) return launch_cgemm_tc(dev, p, st);
     }
     const int N = p.N;
     const long long M = p.rows * kModes;
