@@ -1,0 +1,62 @@
+"""torch.ops.turbofno_b200.spectral_conv{1,2}d: registration and shape function on CPU, results on GPU."""
+import numpy as np
+import pytest
+
+from util import assert_close, oracle_np
+
+
+def test_operators_are_registered_with_a_shape_function():
+    import torch
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    import turbofno_b200.torch_op  # noqa: F401  (registers the operators; loads no CUDA code)
+
+    assert hasattr(torch.ops.turbofno_b200, "spectral_conv1d") and hasattr(torch.ops.turbofno_b200, "spectral_conv2d")
+    with FakeTensorMode():
+        x = torch.empty((3, 16, 256), dtype=torch.complex64)
+        w = torch.empty((16, 64), dtype=torch.complex64)
+        y = torch.ops.turbofno_b200.spectral_conv1d(x, w)
+        assert tuple(y.shape) == (3, 64, 256) and y.dtype == torch.complex64
+        x2 = torch.empty((2, 8, 128, 256), dtype=torch.complex64)
+        w2 = torch.empty((8, 64), dtype=torch.complex64)
+        assert tuple(torch.ops.turbofno_b200.spectral_conv2d(x2, w2).shape) == (2, 64, 128, 256)
+        with pytest.raises(Exception):
+            torch.ops.turbofno_b200.spectral_conv1d(x, w2)      # K mismatch
+
+
+def test_operator_has_no_cpu_kernel():
+    import torch
+
+    import turbofno_b200.torch_op  # noqa: F401
+
+    x = torch.zeros((1, 8, 128), dtype=torch.complex64)
+    w = torch.zeros((8, 64), dtype=torch.complex64)
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        torch.ops.turbofno_b200.spectral_conv1d(x, w)           # the path has no CPU implementation
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,K,N,DY", [(5, 16, 64, 256), (3, 8, 128, 128), (150, 64, 64, 256)])
+def test_spectral_conv1d_operator(cuda, B, K, N, DY):
+    import torch
+
+    import turbofno_b200.torch_op  # noqa: F401
+
+    x, w = oracle_np.make_inputs_1d(B, K, N, DY, seed=B + K)
+    y = torch.ops.turbofno_b200.spectral_conv1d(torch.from_numpy(x).to(cuda), torch.from_numpy(w).to(cuda))
+    assert_close(y.cpu().numpy(), oracle_np.spectral_conv_1d(x, w), "torch op 1d")
+    torch.library.opcheck(torch.ops.turbofno_b200.spectral_conv1d.default,
+                          (torch.from_numpy(x).to(cuda), torch.from_numpy(w).to(cuda)),
+                          test_utils=("test_schema", "test_faketensor"))
+
+
+@pytest.mark.gpu
+def test_spectral_conv2d_operator(cuda):
+    import torch
+
+    import turbofno_b200.torch_op  # noqa: F401
+
+    B, K, N, DX, DY = 2, 16, 64, 128, 256
+    x, w = oracle_np.make_inputs_2d(B, K, N, DX, DY, seed=11)
+    y = torch.ops.turbofno_b200.spectral_conv2d(torch.from_numpy(x).to(cuda), torch.from_numpy(w).to(cuda))
+    assert_close(y.cpu().numpy(), oracle_np.spectral_conv_2d(x, w), "torch op 2d")
