@@ -111,6 +111,15 @@ def test_wide_channels(cuda):
         assert_close(run_1d(cuda, x, w, v), ref, "K=128 N=192 variant " + v)
 
 
+@pytest.mark.parametrize("DY,K", [(256, 16), (256, 32), (256, 48), (256, 64), (128, 32), (128, 64)])
+def test_fused_kernel_chunk_counts_many_rows_per_sm(cuda, DY, K):
+    """One, two, three and four chunks of channels per row (three run on the FP32 kernel), with
+    three to four rows per SM so that every ring stage, S buffer and accumulator buffer is reused."""
+    B, N = 449, 64
+    x, w = oracle_np.make_inputs_1d(B, K, N, DY, seed=DY + K)
+    assert_close(run_1d(cuda, x, w, "D"), oracle_c.spectral_conv_1d(x, w), "fused, %d channels at DY=%d" % (K, DY))
+
+
 def test_alpha_and_as_shipped_second_transform(cuda):
     x, w = oracle_np.make_inputs_1d(4, 16, 64, 256, seed=3)
     a = 1.0 - 1.0j

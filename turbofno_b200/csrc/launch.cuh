@@ -81,7 +81,13 @@ inline bool tc_eligible(const DeviceInfo& dev, int len, const TileParams& p) {
     if (!dev.use_tensor_cores || !dev.status) return false;
     if (p.N != 64 || (len != 128 && len != 256)) return false;
     const int CH = 64 / (len / 64);
-    return p.K >= CH && p.K <= 64 && p.K % CH == 0;
+    if (p.K < CH || p.K > 64 || p.K % CH != 0) return false;
+    // With an odd number (> 1) of chunks per row the two ring stages alternate between the two
+    // forward half-teams, and a half-team would wait on a barrier whose previous phase it has not
+    // seen (a parity wait cannot tell "not yet" from "two phases on"): those shapes (K = 48 at
+    // DY = 256) take the FP32 kernel.
+    const int NC = p.K / CH;
+    return NC == 1 || NC % 2 == 0;
 }
 
 template <int R, bool INVERSE>

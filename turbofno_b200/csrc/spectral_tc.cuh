@@ -8,14 +8,16 @@
 // the two helper warpgroups to the two compute warpgroups (216 each), so that a compute thread
 // can hold a whole 64-point transform in registers:
 //
-//   warps 0,2,4,6  forward  two half-teams {0,4} and {2,6}.  Input rows (DY*8 bytes each) arrive by
-//                           cp.async.bulk in a 3-stage shared-memory ring, CH = 64/R channels per
+//   warps 0,2,4,6  forward  two half-teams {0,2} and {4,6}.  Input rows (DY*8 bytes each) arrive by
+//                           cp.async.bulk in a 2-stage shared-memory ring, CH = 64/R channels per
 //                           stage; a half-team takes one stage, each group of R lanes transforms
 //                           one channel (64-point register FFT + reduce-scatter), splits the 64
 //                           kept modes into tf32 hi/lo parts and stores them as the B operand
-//                           S[mode][kk] (K-major core matrices).
+//                           S[mode][kk] (K-major core matrices) in the half-team's own S buffer.
 //   warps 1,3,5,7  inverse  groups of R lanes read one output channel's 64 modes from the Re/Im
-//                           planes, run the zero-padded inverse transform and store the signal.
+//                           planes and run the zero-padded inverse transform; at DY = 256 the
+//                           rows are staged in shared memory and leave by cp.async.bulk, at
+//                           DY = 128 the lanes store directly.
 //   warps 8-11     hand-off tcgen05.ld of one accumulator row per thread -> Re/Im planes in shared
 //                           memory (a warp may only touch its own quarter of tensor memory, so
 //                           this needs four warps with distinct warp%4).
