@@ -255,13 +255,22 @@ inline int launch_ifft_cols(const DeviceInfo& dev, int len, const ColsParams& p,
 inline size_t image_smem_bytes(int DX, int DY) {
     return ((size_t)DX * kModes + (DX / 64) * 64 + (DY / 64) * 64) * sizeof(float2);
 }
+// 16-byte loads and stores of sample pairs need 16-byte aligned rows
+inline bool image_rows_aligned(const ImageParams& p, bool inverse) {
+    const void* full = inverse ? (const void*)p.out : (const void*)p.in;
+    return (reinterpret_cast<uintptr_t>(full) & 15) == 0 && (p.stride_b & 1) == 0 && (p.stride_k & 1) == 0;
+}
 template <int RX>
 inline int launch_fft2d_rx(const DeviceInfo& dev, int RY, const ImageParams& p, bool inverse, cudaStream_t st) {
     const size_t smem = image_smem_bytes(64 * RX, 64 * RY);
-#define TFNO_IMG(RYV)                                                                              \
-    case RYV:                                                                                      \
-        return inverse ? launch_persistent(dev, ifft2d_pad_kernel<RX, RYV>, smem, p.nimg, p, st)   \
-                       : launch_persistent(dev, fft2d_trunc_kernel<RX, RYV>, smem, p.nimg, p, st);
+    const bool paired = image_rows_aligned(p, inverse);
+#define TFNO_IMG(RYV)                                                                                        \
+    case RYV:                                                                                                \
+        if (paired)                                                                                          \
+            return inverse ? launch_persistent(dev, ifft2d_pad_kernel<RX, RYV, true>, smem, p.nimg, p, st)   \
+                           : launch_persistent(dev, fft2d_trunc_kernel<RX, RYV, true>, smem, p.nimg, p, st); \
+        return inverse ? launch_persistent(dev, ifft2d_pad_kernel<RX, RYV, false>, smem, p.nimg, p, st)      \
+                       : launch_persistent(dev, fft2d_trunc_kernel<RX, RYV, false>, smem, p.nimg, p, st);
     switch (RY) { TFNO_IMG(2) TFNO_IMG(4) }
 #undef TFNO_IMG
     return TFNO_ERR_UNSUPPORTED;
