@@ -260,17 +260,31 @@ inline bool image_rows_aligned(const ImageParams& p, bool inverse) {
     const void* full = inverse ? (const void*)p.out : (const void*)p.in;
     return (reinterpret_cast<uintptr_t>(full) & 15) == 0 && (p.stride_b & 1) == 0 && (p.stride_k & 1) == 0;
 }
+#ifndef TFNO_IMAGE_THREADS
+#define TFNO_IMAGE_THREADS 256
+#endif
+constexpr int kImageThreads = TFNO_IMAGE_THREADS;      // threads of the paired whole-image kernels
+template <int THREADS, typename Kernel>
+inline int launch_image(const DeviceInfo& dev, Kernel kernel, size_t smem, const ImageParams& p, cudaStream_t st) {
+    int occ = 0;
+    int rc = prepare_kernel(kernel, smem, dev, &occ);
+    if (rc != TFNO_OK) return rc;
+    long long grid = (long long)dev.sms * occ;
+    if (grid > p.nimg) grid = p.nimg;
+    kernel<<<(unsigned)grid, THREADS, smem, st>>>(p);
+    return launch_status();
+}
 template <int RX>
 inline int launch_fft2d_rx(const DeviceInfo& dev, int RY, const ImageParams& p, bool inverse, cudaStream_t st) {
     const size_t smem = image_smem_bytes(64 * RX, 64 * RY);
     const bool paired = image_rows_aligned(p, inverse);
-#define TFNO_IMG(RYV)                                                                                        \
-    case RYV:                                                                                                \
-        if (paired)                                                                                          \
-            return inverse ? launch_persistent(dev, ifft2d_pad_kernel<RX, RYV, true>, smem, p.nimg, p, st)   \
-                           : launch_persistent(dev, fft2d_trunc_kernel<RX, RYV, true>, smem, p.nimg, p, st); \
-        return inverse ? launch_persistent(dev, ifft2d_pad_kernel<RX, RYV, false>, smem, p.nimg, p, st)      \
-                       : launch_persistent(dev, fft2d_trunc_kernel<RX, RYV, false>, smem, p.nimg, p, st);
+#define TFNO_IMG(RYV)                                                                                                  \
+    case RYV:                                                                                                          \
+        if (paired)                                                                                                    \
+            return inverse ? launch_image<kImageThreads>(dev, ifft2d_pad_kernel<RX, RYV, true, kImageThreads>, smem, p, st)   \
+                           : launch_image<kImageThreads>(dev, fft2d_trunc_kernel<RX, RYV, true, kImageThreads>, smem, p, st); \
+        return inverse ? launch_image<kThreads>(dev, ifft2d_pad_kernel<RX, RYV, false, kThreads>, smem, p, st)         \
+                       : launch_image<kThreads>(dev, fft2d_trunc_kernel<RX, RYV, false, kThreads>, smem, p, st);
     switch (RY) { TFNO_IMG(2) TFNO_IMG(4) }
 #undef TFNO_IMG
     return TFNO_ERR_UNSUPPORTED;

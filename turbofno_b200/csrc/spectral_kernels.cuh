@@ -95,7 +95,7 @@ TFNO_D void load_decimated_paired(float2 (&v)[64], const float2* __restrict__ si
 }
 
 template <int R>
-TFNO_D void store_decimated_paired(const float2 (&v)[64], float2* __restrict__ sig, int j1) {
+TFNO_D void store_decimated_paired(const float2 (&v)[64], float2* __restrict__ sig, int j1, bool live = true) {
     const bool odd = (j1 & 1) != 0;
     float2* base = sig + (odd ? R : 0) + (j1 & ~1);
 #pragma unroll
@@ -107,7 +107,7 @@ TFNO_D void store_decimated_paired(const float2 (&v)[64], float2* __restrict__ s
         got.x = __shfl_xor_sync(0xffffffffu, send.x, 1);
         got.y = __shfl_xor_sync(0xffffffffu, send.y, 1);
         const float4 q = odd ? make_float4(got.x, got.y, odd_j2.x, odd_j2.y) : make_float4(even_j2.x, even_j2.y, got.x, got.y);
-        *reinterpret_cast<float4*>(base + 2 * R * n2) = q;
+        if (live) *reinterpret_cast<float4*>(base + 2 * R * n2) = q;
     }
 }
 
@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(kThreads, 1) spectral_tile_kernel(TileParams p
                 const bool live = k0 + g < K;
                 const int k = live ? k0 + g : K - 1;
                 float2 v[64];
-                load_decimated<R>(v, p.x + row * p.x_stride_row + (long long)k * p.x_stride_k, 1, r);
+                load_decimated_paired<R>(v, p.x + row * p.x_stride_row + (long long)k * p.x_stride_k, r);
                 forward_trunc<R>(v, twF, r);
                 if (live) store_modes_to_tile<R>(v, sA, k, r);
             }
@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(kThreads, 1) spectral_tile_kernel(TileParams p
                     }
                     if (p.conj_inverse) inverse_pad_lane<+1, R>(v, twI, j1);
                     else inverse_pad_lane<-1, R>(v, twI, j1);
-                    store_decimated<R>(v, p.y + row * p.y_stride_row + (long long)n * p.y_stride_n, 1, j1);
+                    store_decimated_paired<R>(v, p.y + row * p.y_stride_row + (long long)n * p.y_stride_n, j1);   // whole warps: N is a multiple of 64
                 }
             }
             __syncthreads();   // sC and sA are rewritten by the next row
@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1) fft_rows_trunc_kernel(RowsParams 
         const bool live = s < p.nsig;
         if (!live) s = p.nsig - 1;
         float2 v[64];
-        load_decimated<R>(v, p.in + (s % p.per_k) * p.stride_row + (s / p.per_k) * p.stride_k, 1, r);
+        load_decimated_paired<R>(v, p.in + (s % p.per_k) * p.stride_row + (s / p.per_k) * p.stride_k, r);
         forward_trunc<R>(v, twF, r);
         if (live) {
             float2* dst = p.out + s * kModes + PER * r;
@@ -345,8 +345,10 @@ __global__ void __launch_bounds__(kThreads, 1) ifft_rows_pad_kernel(RowsParams p
     const int g = threadIdx.x / R, j1 = threadIdx.x % R;
     const long long nblk = (p.nsig + GROUPS - 1) / GROUPS;
     for (long long blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
+        // clamp instead of branching so that every lane of a warp takes part in the store's shuffles
         long long s = blk * GROUPS + g;
-        if (s >= p.nsig) continue;
+        const bool live = s < p.nsig;
+        if (!live) s = p.nsig - 1;
         float2 v[64];
         const float4* src = reinterpret_cast<const float4*>(p.in + s * kModes);
 #pragma unroll
@@ -357,7 +359,7 @@ __global__ void __launch_bounds__(kThreads, 1) ifft_rows_pad_kernel(RowsParams p
         }
         if (p.conj_inverse) inverse_pad_lane<+1, R>(v, twI, j1);
         else inverse_pad_lane<-1, R>(v, twI, j1);
-        store_decimated<R>(v, p.out + (s % p.per_k) * p.stride_row + (s / p.per_k) * p.stride_k, 1, j1);
+        store_decimated_paired<R>(v, p.out + (s % p.per_k) * p.stride_row + (s / p.per_k) * p.stride_k, j1, live);
     }
 }
 
@@ -448,25 +450,26 @@ __device__ __forceinline__ void prefetch_l2_block(const void* base, int bytes, i
     for (int off = tid * 128; off < bytes; off += nthreads * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(b + off));
 }
 
-template <int RX, int RY, bool PAIRED>
-__global__ void __launch_bounds__(kThreads, 1) fft2d_trunc_kernel(ImageParams p) {
+template <int RX, int RY, bool PAIRED, int THREADS>
+__global__ void __launch_bounds__(THREADS, 1) fft2d_trunc_kernel(ImageParams p) {
     constexpr int DX = 64 * RX, DY = 64 * RY;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float2* sY = reinterpret_cast<float2*>(smem_raw);          // [DX][64] swizzled
     float2* twY = sY + DX * kModes;                             // [RY][64]
     float2* twX = twY + RY * 64;                                // [RX][64]
     const int tid = threadIdx.x;
-    fill_forward_table<RY>(twY, tid, kThreads);
-    fill_forward_table<RX>(twX, tid, kThreads);
+    fill_forward_table<RY>(twY, tid, THREADS);
+    fill_forward_table<RX>(twX, tid, THREADS);
     __syncthreads();
     for (long long img = blockIdx.x; img < p.nimg; img += gridDim.x) {
         const float2* src = p.in + (img % p.per_k) * p.stride_b + (img / p.per_k) * p.stride_k;
         {
-            constexpr int GROUPS = kThreads / RY;
+            constexpr int GROUPS = THREADS / RY;
             const int g = tid / RY, r = tid % RY;
 #pragma unroll 1
             for (int x0 = 0; x0 < DX; x0 += GROUPS) {
                 const int x = x0 + g;
+                if (x >= DX) continue;          // last round of a thread count that does not divide DX; whole warps
                 float2 v[64];
                 if constexpr (PAIRED) load_decimated_paired<RY>(v, src + (long long)x * DY, r);
                 else load_decimated<RY>(v, src + (long long)x * DY, 1, r);
@@ -474,10 +477,11 @@ __global__ void __launch_bounds__(kThreads, 1) fft2d_trunc_kernel(ImageParams p)
                 // of this CTA's next image) travel from DRAM to the L2: a warp has no other loads
                 // in flight while it computes, and only two warps share a scheduler.
                 if (x0 + GROUPS < DX) {
-                    prefetch_l2_block(src + (long long)(x0 + GROUPS) * DY, GROUPS * DY * 8, tid, kThreads);
+                    const int next_rows = (DX - (x0 + GROUPS) < GROUPS) ? DX - (x0 + GROUPS) : GROUPS;      // stay inside the image
+                    prefetch_l2_block(src + (long long)(x0 + GROUPS) * DY, next_rows * DY * 8, tid, THREADS);
                 } else if (img + gridDim.x < p.nimg) {
                     const long long nx = img + gridDim.x;
-                    prefetch_l2_block(p.in + (nx % p.per_k) * p.stride_b + (nx / p.per_k) * p.stride_k, GROUPS * DY * 8, tid, kThreads);
+                    prefetch_l2_block(p.in + (nx % p.per_k) * p.stride_b + (nx / p.per_k) * p.stride_k, GROUPS * DY * 8, tid, THREADS);
                 }
                 forward_trunc<RY>(v, twY, r);
                 store_modes_to_tile<RY>(v, sY, x, r);
@@ -485,7 +489,7 @@ __global__ void __launch_bounds__(kThreads, 1) fft2d_trunc_kernel(ImageParams p)
         }
         __syncthreads();
         {
-            constexpr int GROUPS = kThreads / RX, PER = 64 / RX;
+            constexpr int GROUPS = THREADS / RX, PER = 64 / RX;
             const int g = tid / RX, r = tid % RX;
             float2* dst = p.out + img * (long long)(kModes * kModes);
 #pragma unroll 1
@@ -505,22 +509,22 @@ __global__ void __launch_bounds__(kThreads, 1) fft2d_trunc_kernel(ImageParams p)
 }
 
 // [image][64][64] -> zero-pad -> inverse along X into shared memory -> inverse along Y -> [image][DX][DY]
-template <int RX, int RY, bool PAIRED>
-__global__ void __launch_bounds__(kThreads, 1) ifft2d_pad_kernel(ImageParams p) {
+template <int RX, int RY, bool PAIRED, int THREADS>
+__global__ void __launch_bounds__(THREADS, 1) ifft2d_pad_kernel(ImageParams p) {
     constexpr int DX = 64 * RX, DY = 64 * RY;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float2* sY = reinterpret_cast<float2*>(smem_raw);          // [DX][64] swizzled
     float2* twY = sY + DX * kModes;
     float2* twX = twY + RY * 64;
     const int tid = threadIdx.x;
-    fill_inverse_table<RY>(twY, tid, kThreads, make_float2(1.f, 0.f), p.conj_inverse != 0);
-    fill_inverse_table<RX>(twX, tid, kThreads, p.gain, p.conj_inverse != 0);
+    fill_inverse_table<RY>(twY, tid, THREADS, make_float2(1.f, 0.f), p.conj_inverse != 0);
+    fill_inverse_table<RX>(twX, tid, THREADS, p.gain, p.conj_inverse != 0);
     __syncthreads();
     for (long long img = blockIdx.x; img < p.nimg; img += gridDim.x) {
         const float2* src = p.in + img * (long long)(kModes * kModes);
         float2* dst = p.out + (img % p.per_k) * p.stride_b + (img / p.per_k) * p.stride_k;
         {
-            constexpr int GROUPS = kThreads / RX;
+            constexpr int GROUPS = THREADS / RX;
             const int g = tid / RX, j1 = tid % RX;
 #pragma unroll 1
             for (int c0 = 0; c0 < kModes; c0 += GROUPS) {
@@ -537,11 +541,12 @@ __global__ void __launch_bounds__(kThreads, 1) ifft2d_pad_kernel(ImageParams p) 
         }
         __syncthreads();
         {
-            constexpr int GROUPS = kThreads / RY;
+            constexpr int GROUPS = THREADS / RY;
             const int g = tid / RY, j1 = tid % RY;
 #pragma unroll 1
             for (int x0 = 0; x0 < DX; x0 += GROUPS) {
                 const int x = x0 + g;
+                if (x >= DX) continue;          // whole warps, as in the forward kernel
                 float2 v[64];
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {

@@ -101,7 +101,10 @@ template <int R> struct Geometry {
     static constexpr int KSTEPS_PER_CHUNK = 2 * CH / 8;
     // Output rows are staged in shared memory and leave through the bulk-copy engine when there is
     // room (DY = 256); at DY = 128 the S buffers are twice as large and the lanes store directly.
-    static constexpr bool STAGED_OUT = (R == 4);
+#ifndef TFNO_STAGED_OUT
+#define TFNO_STAGED_OUT 1
+#endif
+    static constexpr bool STAGED_OUT = (R == 4) && (TFNO_STAGED_OUT != 0);
     static constexpr int OUT_ROWS = 32 / R;                 // output rows staged per inverse warp and task
     static constexpr int OUT_STRIDE = ROW_BYTES + 16;       // padded like the input rows
     static constexpr int OUT_BYTES = STAGED_OUT ? OUT_ROWS * OUT_STRIDE : 0;   // per inverse warp
@@ -544,11 +547,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 // the load/store unit.  The lanes that issue the copies first wait until their
                 // previous copies have finished reading the staging buffer.
                 if constexpr (!G::STAGED_OUT) {
-                    float2* dst = p.y + row * p.y_stride_row + (long long)n * p.y_stride_n;
+                    // Lanes r and r ^ 1 of a group (GPW lanes apart) own samples that alternate in
+                    // memory: each stores 16 bytes (its own sample and the neighbour's) for every
+                    // second j2 and they swap the foreign halves with a shuffle -- half as many
+                    // store instructions, each filling whole 32-byte sectors.
+                    const bool odd = (r & 1) != 0;
+                    float2* dst = p.y + row * p.y_stride_row + (long long)n * p.y_stride_n + (odd ? R : 0) + (r & ~1);
 #pragma unroll
-                    for (int j2 = 0; j2 < 64; ++j2) {
-                        const float2 o = v[slot(j2)];
-                        dst[R * j2 + r] = INVERSE ? make_float2(o.y, o.x) : o;
+                    for (int n2 = 0; n2 < 32; ++n2) {
+                        const float2 a = v[slot(2 * n2)], b = v[slot(2 * n2 + 1)];
+                        const float2 ev = INVERSE ? make_float2(a.y, a.x) : a;       // this lane's sample R*(2*n2) + r
+                        const float2 od = INVERSE ? make_float2(b.y, b.x) : b;       // this lane's sample R*(2*n2+1) + r
+                        const float2 send = odd ? ev : od;
+                        float2 got;
+                        got.x = __shfl_xor_sync(0xffffffffu, send.x, GPW);
+                        got.y = __shfl_xor_sync(0xffffffffu, send.y, GPW);
+                        *reinterpret_cast<float4*>(dst + 2 * R * n2) =
+                            odd ? make_float4(got.x, got.y, od.x, od.y) : make_float4(ev.x, ev.y, got.x, got.y);
                     }
                 } else {
                 unsigned char* ost = ostage + qi * G::OUT_BYTES;
