@@ -120,6 +120,13 @@ def test_fused_kernel_chunk_counts_many_rows_per_sm(cuda, DY, K):
     assert_close(run_1d(cuda, x, w, "D"), oracle_c.spectral_conv_1d(x, w), "fused, %d channels at DY=%d" % (K, DY))
 
 
+def test_wide_layer_runs_the_fused_kernel_per_block_of_64_outputs(cuda):
+    # N = 128 and 192 with enough rows for the tensor-core kernel (two rows per SM and more)
+    for (B, K, N, DY) in [(300, 32, 128, 256), (300, 64, 192, 128)]:
+        x, w = oracle_np.make_inputs_1d(B, K, N, DY, seed=N + DY)
+        assert_close(run_1d(cuda, x, w, "D"), oracle_c.spectral_conv_1d(x, w), "wide layer %s" % ((B, K, N, DY),))
+
+
 def test_alpha_and_as_shipped_second_transform(cuda):
     x, w = oracle_np.make_inputs_1d(4, 16, 64, 256, seed=3)
     a = 1.0 - 1.0j

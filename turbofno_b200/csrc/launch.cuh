@@ -75,11 +75,13 @@ inline int launch_tile_r(const DeviceInfo& dev, int R, const TileParams& p, cuda
     return TFNO_ERR_UNSUPPORTED;
 }
 
-// Tensor-core fused kernel: N = 64, K a multiple of the chunk size (64/R channels) up to 64,
+// Tensor-core fused kernel: N a multiple of 64 (64 per launch), K a multiple of the chunk size (64/R channels) up to 64,
 // transform length 128 or 256.
 inline bool tc_eligible(const DeviceInfo& dev, int len, const TileParams& p) {
     if (!dev.use_tensor_cores || !dev.status) return false;
-    if (p.N != 64 || (len != 128 && len != 256)) return false;
+    if (p.N % 64 != 0 || (len != 128 && len != 256)) return false;
+    // N > 64 takes one launch per 64 output channels: worth it only when the launches are long
+    if (p.N > 64 && p.rows < 2LL * dev.sms) return false;
     const int CH = 64 / (len / 64);
     if (p.K < CH || p.K > 64 || p.K % CH != 0) return false;
     // With an odd number (> 1) of chunks per row the two ring stages alternate between the two
@@ -174,8 +176,20 @@ inline int launch_tile(const DeviceInfo& dev, int len, TileParams p, cudaStream_
     if ((FWD || INV) && !supported_len(len)) return TFNO_ERR_UNSUPPORTED;
     if constexpr (FWD && INV) {
         if (tc_eligible(dev, len, p)) {
-            if (p.conj_inverse) return len == 128 ? launch_tc_inst<2, true>(dev, p, st) : launch_tc_inst<4, true>(dev, p, st);
-            return len == 128 ? launch_tc_inst<2, false>(dev, p, st) : launch_tc_inst<4, false>(dev, p, st);
+            // The tensor-core kernel produces 64 output channels (its 128 accumulator rows); wider
+            // layers run it once per block of 64, re-reading the input (still faster than the FP32
+            // kernel: 1.0 against 1.7 ms at bs=8192, K=64, N=128, DY=256).
+            for (int n0 = 0; n0 < p.N; n0 += 64) {
+                TileParams q = p;
+                q.N = 64;
+                q.w = p.w + (long long)n0 * p.w_stride_n;
+                q.y = p.y + (long long)n0 * p.y_stride_n;
+                int rc;
+                if (q.conj_inverse) rc = len == 128 ? launch_tc_inst<2, true>(dev, q, st) : launch_tc_inst<4, true>(dev, q, st);
+                else rc = len == 128 ? launch_tc_inst<2, false>(dev, q, st) : launch_tc_inst<4, false>(dev, q, st);
+                if (rc != TFNO_OK) return rc;
+            }
+            return TFNO_OK;
         }
     }
     if constexpr (!FWD && !INV) {
