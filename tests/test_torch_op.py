@@ -60,3 +60,36 @@ def test_spectral_conv2d_operator(cuda):
     x, w = oracle_np.make_inputs_2d(B, K, N, DX, DY, seed=11)
     y = torch.ops.turbofno_b200.spectral_conv2d(torch.from_numpy(x).to(cuda), torch.from_numpy(w).to(cuda))
     assert_close(y.cpu().numpy(), oracle_np.spectral_conv_2d(x, w), "torch op 2d")
+
+
+@pytest.mark.gpu
+def test_spectral_conv1d_gradients_match_autograd_through_torch_fft(cuda):
+    """grad_x and grad_W of the operator (own kernels) against autograd through a torch.fft
+    restatement of the layer, for a real-valued loss; complex64, so the parity tolerance."""
+    import torch
+
+    import turbofno_b200.torch_op  # noqa: F401
+
+    B, K, N, DY = 6, 64, 64, 256
+    x0, w0 = oracle_np.make_inputs_1d(B, K, N, DY, seed=5)
+    rng = np.random.default_rng(9)
+    t0 = (rng.standard_normal((B, N, DY)) + 1j * rng.standard_normal((B, N, DY))).astype(np.complex64)
+    target = torch.from_numpy(t0).to(cuda)
+
+    def loss_of(y):
+        return (y - target).abs().pow(2).sum()
+
+    x = torch.from_numpy(x0).to(cuda).requires_grad_(True)
+    w = torch.from_numpy(w0).to(cuda).requires_grad_(True)
+    loss_of(torch.ops.turbofno_b200.spectral_conv1d(x, w)).backward()
+
+    xr = torch.from_numpy(x0).to(cuda).requires_grad_(True)
+    wr = torch.from_numpy(w0).to(cuda).requires_grad_(True)
+    spec = torch.fft.fft(xr, dim=-1)[..., :64]
+    yhat = torch.einsum("bkm,kn->bnm", spec, wr)
+    padded = torch.zeros((B, N, DY), dtype=torch.complex64, device=cuda)
+    padded = torch.cat([yhat, padded[..., 64:]], dim=-1)
+    loss_of(torch.fft.ifft(padded, dim=-1)).backward()
+
+    assert_close(x.grad.cpu().numpy(), xr.grad.cpu().numpy(), "grad_x")
+    assert_close(w.grad.cpu().numpy(), wr.grad.cpu().numpy(), "grad_W")

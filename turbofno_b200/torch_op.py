@@ -12,8 +12,14 @@ fusion_variants/2D_D_exp_fused_fft_cgemm_ifft/), which has no framework binding 
 
 The operators are registered with torch.library, so they carry a shape function for tracing and
 export; they run on the caller's current stream and allocate only their output and, in 2D, the
-plan's workspace through the caching allocator.  Inference only: no autograd formula is
-registered.  Plans are cached per (shape, device).
+plan's workspace through the caching allocator.  Plans are cached per (shape, device).
+
+spectral_conv1d has an autograd formula built from the same kernels: the layer is
+y = A(x) W with A = (1/DY) F^H P F (P keeps 64 modes), A is self-adjoint, so
+grad_x = spectral_conv1d(grad_y, W^H) -- which needs the kernel's shape limits for the swapped
+channel counts (K a multiple of 64, N a multiple of 8) -- and grad_W = X^H G / DY per mode, summed
+over batch and modes, with X, G the truncated spectra of x and grad_y from the stand-alone
+transform kernel (tfno_fft_stride_DY).  spectral_conv2d is forward only.
 """
 import torch
 
@@ -72,3 +78,31 @@ def spectral_conv2d(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 def _(x, w):
     _check(x, w, 2)
     return x.new_empty((x.shape[0], w.shape[1], x.shape[2], x.shape[3]))
+
+
+def _truncated_spectrum(t):
+    """[B, C, DY] -> [B, C, 64]: forward transform of every signal, first 64 modes (tfno_fft_stride_DY)."""
+    B, C, DY = t.shape
+    out = torch.empty((B, C, 64), dtype=torch.complex64, device=t.device)
+    api.fft_stride_DY(t.contiguous(), out, B * C, DY)
+    return out
+
+
+def _conv1d_setup_context(ctx, inputs, output):
+    x, w = inputs
+    ctx.save_for_backward(x, w)
+
+
+def _conv1d_backward(ctx, grad_y):
+    x, w = ctx.saved_tensors
+    grad_x = grad_w = None
+    grad_y = grad_y.contiguous()
+    if ctx.needs_input_grad[0]:
+        grad_x = spectral_conv1d(grad_y, w.conj().transpose(0, 1).contiguous())
+    if ctx.needs_input_grad[1]:
+        X, G = _truncated_spectrum(x), _truncated_spectrum(grad_y)
+        grad_w = torch.einsum("bkm,bnm->kn", X.conj(), G) / x.shape[2]
+    return grad_x, grad_w
+
+
+spectral_conv1d.register_autograd(_conv1d_backward, setup_context=_conv1d_setup_context)
