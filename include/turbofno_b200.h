@@ -91,6 +91,12 @@ int tfno_destroy(tfno_handle* h);
  * inside a kernel (the kernel then stops early and its output is incomplete).  Synchronises the
  * device.  The reference has no counterpart: its kernels contain no waits. */
 int tfno_device_status(tfno_handle* h, int* out);
+/* Sets the status word back to 0 (after the caller has dealt with a reported time-out). */
+int tfno_device_status_reset(tfno_handle* h);
+/* Launches one warp that waits on a barrier nothing completes: the wait gives up after its limit
+ * (one second), the kernel returns normally and tfno_device_status then reads 99.  Shows that a
+ * kernel-side wait of this library cannot hang the device; no counterpart in the reference. */
+int tfno_selftest_bounded_wait(tfno_handle* h, void* stream);
 /* number of SMs of the handle's device (148 on B200); grids are sized from it */
 int tfno_sm_count(const tfno_handle* h, int* out);
 

@@ -118,3 +118,27 @@ def test_partial_fusions(cuda, DY):
     out2 = torch.empty((N, B, DY), dtype=torch.complex64, device=cuda)
     t.fused_fft_cgemm_ifft(M, N, K, xd, wd, None, out2, DY=DY)
     assert_close(np.swapaxes(out2.cpu().numpy(), 0, 1), yref, "fused_fft_cgemm_ifft")
+
+
+def test_a_kernel_side_wait_that_runs_out_reports_a_status_and_leaves_the_device_usable(cuda):
+    """Every wait inside the kernels is bounded; this makes one run out on purpose (a barrier that
+    nothing completes) without any fault: the kernel returns, the status word carries the code, and
+    the next layer on the same context is right."""
+    import time
+
+    import torch
+    import turbofno_b200 as t
+
+    h = t.Handle.get(0)
+    assert h.device_status == 0
+    t0 = time.perf_counter()
+    h.selftest_bounded_wait()
+    assert h.device_status == 99                      # reading the status synchronises
+    assert 0.5 < time.perf_counter() - t0 < 30.0      # the one-second limit, not the spin-count backstop
+    h.reset_device_status()
+    assert h.device_status == 0
+    x, w = oracle_np.make_inputs_1d(3, 16, 64, 256, seed=2)
+    plan = t.SpectralConv(1, 3, 256, 16, 64, variant="D")
+    y = plan(_dev(cuda, np.swapaxes(x, 0, 1)), _dev(cuda, w.T))
+    assert_close(np.swapaxes(y.cpu().numpy(), 0, 1), oracle_np.spectral_conv_1d(x, w), "layer after a timed-out wait")
+    assert h.device_status == 0

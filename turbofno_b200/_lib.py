@@ -49,6 +49,8 @@ SYMBOLS = {
     "tfno_destroy": (_i, [_vp]),
     "tfno_sm_count": (_i, [_vp, ctypes.POINTER(_i)]),
     "tfno_device_status": (_i, [_vp, ctypes.POINTER(_i)]),
+    "tfno_device_status_reset": (_i, [_vp]),
+    "tfno_selftest_bounded_wait": (_i, [_vp, _vp]),
     "tfno_plan_create": (_i, [_vp, ctypes.POINTER(Problem), ctypes.POINTER(_vp)]),
     "tfno_plan_destroy": (_i, [_vp]),
     "tfno_workspace_bytes": (ctypes.c_size_t, [_vp]),

@@ -62,6 +62,13 @@ class Handle:
         check(self.lib.tfno_device_status(self._h, ctypes.byref(n)), "tfno_device_status")
         return n.value
 
+    def reset_device_status(self):
+        check(self.lib.tfno_device_status_reset(self._h), "tfno_device_status_reset")
+
+    def selftest_bounded_wait(self, stream=None):
+        """Makes one kernel-side wait run out (about one second); device_status then reads 99."""
+        check(self.lib.tfno_selftest_bounded_wait(self._h, _stream_ptr(stream)), "tfno_selftest_bounded_wait")
+
     def close(self):
         if self._h:
             self.lib.tfno_destroy(self._h)

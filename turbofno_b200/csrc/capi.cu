@@ -189,6 +189,40 @@ int tfno_device_status(tfno_handle* h, int* out) {
     return TFNO_OK;
 }
 
+int tfno_device_status_reset(tfno_handle* h) {
+    if (!h) return TFNO_ERR_INVALID_ARG;
+    DeviceGuard guard(h->dev.device);
+    if (!guard.ok || cudaMemset(h->dev.status, 0, sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        return TFNO_ERR_CUDA;
+    }
+    return TFNO_OK;
+}
+
+// One warp waits on a barrier that nothing ever completes.  The wait gives up after its limit (one
+// second), records code 99 in the status word and the kernel returns normally: the error path of
+// every kernel-side wait of this library, made to happen without any fault.
+__global__ void bounded_wait_selftest_kernel(int* status) {
+    __shared__ uint64_t bar_storage;
+    __shared__ int abort_storage;
+    const uint32_t bar = tc::smem_u32(&bar_storage);
+    if (threadIdx.x == 0) {
+        tc::mbar_init(bar, 1);
+        abort_storage = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    tc::mbar_wait(bar, 0, &abort_storage, status, 99, tc::kHelperIdleNs);
+}
+
+int tfno_selftest_bounded_wait(tfno_handle* h, void* stream) {
+    if (!h) return TFNO_ERR_INVALID_ARG;
+    DeviceGuard guard(h->dev.device);
+    if (!guard.ok) return TFNO_ERR_CUDA;
+    bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(h->dev.status);
+    return launch_status();
+}
+
 int tfno_sm_count(const tfno_handle* h, int* out) {
     if (!h || !out) return TFNO_ERR_INVALID_ARG;
     *out = h->dev.sms;
