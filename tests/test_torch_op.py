@@ -93,3 +93,32 @@ def test_spectral_conv1d_gradients_match_autograd_through_torch_fft(cuda):
 
     assert_close(x.grad.cpu().numpy(), xr.grad.cpu().numpy(), "grad_x")
     assert_close(w.grad.cpu().numpy(), wr.grad.cpu().numpy(), "grad_W")
+
+
+@pytest.mark.gpu
+def test_spectral_conv2d_gradients_match_autograd_through_torch_fft(cuda):
+    import torch
+
+    import turbofno_b200.torch_op  # noqa: F401
+
+    B, K, N, DX, DY = 2, 64, 64, 128, 256
+    x0, w0 = oracle_np.make_inputs_2d(B, K, N, DX, DY, seed=6)
+    rng = np.random.default_rng(10)
+    target = torch.from_numpy((rng.standard_normal((B, N, DX, DY)) + 1j * rng.standard_normal((B, N, DX, DY))).astype(np.complex64)).to(cuda)
+
+    def loss_of(y):
+        return (y - target).abs().pow(2).sum()
+
+    x = torch.from_numpy(x0).to(cuda).requires_grad_(True)
+    w = torch.from_numpy(w0).to(cuda).requires_grad_(True)
+    loss_of(torch.ops.turbofno_b200.spectral_conv2d(x, w)).backward()
+
+    xr = torch.from_numpy(x0).to(cuda).requires_grad_(True)
+    wr = torch.from_numpy(w0).to(cuda).requires_grad_(True)
+    spec = torch.fft.fft2(xr, dim=(-2, -1))[..., :64, :64]
+    yhat = torch.einsum("bkxy,kn->bnxy", spec, wr)
+    padded = torch.nn.functional.pad(torch.view_as_real(yhat), (0, 0, 0, DY - 64, 0, DX - 64))
+    loss_of(torch.fft.ifft2(torch.view_as_complex(padded.contiguous()), dim=(-2, -1))).backward()
+
+    assert_close(x.grad.cpu().numpy(), xr.grad.cpu().numpy(), "grad_x (2D)")
+    assert_close(w.grad.cpu().numpy(), wr.grad.cpu().numpy(), "grad_W (2D)")

@@ -14,12 +14,13 @@ The operators are registered with torch.library, so they carry a shape function 
 export; they run on the caller's current stream and allocate only their output and, in 2D, the
 plan's workspace through the caching allocator.  Plans are cached per (shape, device).
 
-spectral_conv1d has an autograd formula built from the same kernels: the layer is
+Both operators have an autograd formula built from the same kernels: the layer is
 y = A(x) W with A = (1/DY) F^H P F (P keeps 64 modes), A is self-adjoint, so
 grad_x = spectral_conv1d(grad_y, W^H) -- which needs the kernel's shape limits for the swapped
 channel counts (K a multiple of 64, N a multiple of 8) -- and grad_W = X^H G / DY per mode, summed
 over batch and modes, with X, G the truncated spectra of x and grad_y from the stand-alone
-transform kernel (tfno_fft_stride_DY).  spectral_conv2d is forward only.
+transform kernels (tfno_fft_stride_DY; in 2D tfno_fft_stride along X first).  The same holds for
+spectral_conv2d with 1/(DX*DY).
 """
 import torch
 
@@ -106,3 +107,28 @@ def _conv1d_backward(ctx, grad_y):
 
 
 spectral_conv1d.register_autograd(_conv1d_backward, setup_context=_conv1d_setup_context)
+
+
+def _truncated_spectrum2d(t):
+    """[B, C, DX, DY] -> [B, C, 64, 64]: X transform keeping 64 modes (tfno_fft_stride), then Y."""
+    B, C, DX, DY = t.shape
+    tx = torch.empty((B, C, 64, DY), dtype=torch.complex64, device=t.device)
+    api.fft_stride(t.contiguous(), tx, DY, B * C * DY, DX)
+    out = torch.empty((B, C, 64, 64), dtype=torch.complex64, device=t.device)
+    api.fft_stride_DY(tx, out, B * C * 64, DY)
+    return out
+
+
+def _conv2d_backward(ctx, grad_y):
+    x, w = ctx.saved_tensors
+    grad_x = grad_w = None
+    grad_y = grad_y.contiguous()
+    if ctx.needs_input_grad[0]:
+        grad_x = spectral_conv2d(grad_y, w.conj().transpose(0, 1).contiguous())
+    if ctx.needs_input_grad[1]:
+        X, G = _truncated_spectrum2d(x), _truncated_spectrum2d(grad_y)
+        grad_w = torch.einsum("bkxy,bnxy->kn", X.conj(), G) / (x.shape[2] * x.shape[3])
+    return grad_x, grad_w
+
+
+spectral_conv2d.register_autograd(_conv2d_backward, setup_context=_conv1d_setup_context)
