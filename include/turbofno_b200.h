@@ -74,6 +74,11 @@ typedef struct {
                                       transform forward, as the reference drivers do
                                       (fusion_variants/1D_E_baseline/fused.cu:190)                   */
     int scale_inverse;        /* 1: multiply by 1/DY (1D) or 1/(DX*DY) (2D); 0: unnormalised        */
+    int x_modes_centered;     /* 2D, variant D: keep X modes -32..31 (low positive AND low negative
+                                 frequencies, what an FNO layer keeps along a non-last axis) instead
+                                 of the reference's corner 0..63
+                                 (fusion_variants/2D_E_baseline/fused_trunc_2D.cu:30-39); Y modes
+                                 stay 0..63.  0 = reference behaviour.                               */
 } tfno_problem;
 
 typedef struct tfno_handle_s tfno_handle;   /* one per device                                      */

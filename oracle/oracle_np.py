@@ -71,15 +71,19 @@ def ifft_pad_1d(c, DY, scale=True):
     return y if scale else y * DY
 
 
-def spectral_conv_2d(x, w, modes=MODES, alpha=1.0, inverse=True, scale=True):
+def spectral_conv_2d(x, w, modes=MODES, alpha=1.0, inverse=True, scale=True, x_modes_centered=False):
+    """x_modes_centered: keep X modes -modes/2 .. modes/2-1 (both low-frequency blocks of a
+    non-last axis, as an FNO layer does) instead of the reference's corner 0 .. modes-1
+    (fusion_variants/2D_E_baseline/fused_trunc_2D.cu:30-39); an extension, not reference behaviour."""
     x = np.asarray(x, dtype=np.complex128)
     w = np.asarray(w, dtype=np.complex128)
     B, K, DX, DY = x.shape
     N = w.shape[1]
-    X = np.fft.fft2(x, axes=(-2, -1))[..., :modes, :modes]   # [B,K,modes,modes]
+    kx = (np.arange(-modes // 2, modes // 2) % DX) if x_modes_centered else np.arange(modes)
+    X = np.fft.fft2(x, axes=(-2, -1))[..., kx, :][..., :modes]   # [B,K,modes,modes]
     C = np.einsum("bkxy,kn->bnxy", X, w) * alpha
     P = np.zeros((B, N, DX, DY), dtype=np.complex128)
-    P[..., :modes, :modes] = C
+    P[..., kx, :modes] = C
     if inverse:
         y = np.fft.ifft2(P, axes=(-2, -1))
         if not scale:

@@ -114,3 +114,26 @@ def test_config4_chain_full_size_sampled(cuda):
     # four chained single-precision layers against a chain that rounds to complex64 between layers
     assert_close(got, ref, "config 4 chain", max_rel=1e-4, rel_l2=1e-5)
     plan.close()
+
+
+@pytest.mark.parametrize("DX,DY", [(128, 128), (256, 256), (128, 256), (256, 128)])
+def test_centered_x_modes(cuda, DX, DY):
+    """Extension beyond the reference: X modes -32..31 instead of 0..63 (variant D, 2D)."""
+    import torch
+    import turbofno_b200 as t
+
+    bs, K, N = 3, 16, 64
+    x, w = oracle_np.make_inputs_2d(bs, K, N, DX, DY, seed=DX + DY)
+    plan = t.SpectralConv(2, bs, DY, K, N, DX=DX, variant="D", x_modes_centered=True)
+    y = plan(torch.from_numpy(to_reference_layout(x)).to(cuda), torch.from_numpy(w_reference_layout(w)).to(cuda))
+    ref = oracle_np.spectral_conv_2d(x, w, x_modes_centered=True)
+    assert_close(np.swapaxes(y.cpu().numpy(), 0, 1), ref, "centered X modes %dx%d" % (DX, DY))
+    # and it is not the corner selection
+    corner = oracle_np.spectral_conv_2d(x, w)
+    assert np.abs(ref - corner).max() > 1e-2
+    plan.close()
+    # only the whole-image kernels of variant D know this mode set
+    from turbofno_b200 import _lib
+    with pytest.raises(t.TfnoError) as e:
+        t.SpectralConv(2, bs, DY, K, N, DX=DX, variant="A", x_modes_centered=True)
+    assert e.value.status == _lib.ERR_UNSUPPORTED

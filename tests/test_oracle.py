@@ -116,3 +116,22 @@ def test_c_oracle_against_golden():
     assert oracle_np.errors(oracle_c.spectral_conv_1d(g["x"], g["w"])[:, ::8, :], g["y"])[0] < 1e-12
     g = np.load(os.path.join(GOLDEN, "c2_2d_bs1_k8_n64_128x256.npz"))
     assert oracle_np.errors(oracle_c.spectral_conv_2d(g["x"], g["w"])[:, ::8, ::8, ::8], g["y"])[0] < 1e-12
+
+
+def test_centered_x_modes_keep_negative_frequencies():
+    """A plane wave with X frequency -5 passes a layer with identity weights when the centered X
+    mode set (-32..31) is kept, and is removed by the reference's corner set (0..63)."""
+    DX = DY = 128
+    xx, yy = np.meshgrid(np.arange(DX), np.arange(DY), indexing="ij")
+    wave = np.exp(2j * np.pi * (-5 * xx / DX + 3 * yy / DY))
+    x = np.zeros((1, 8, DX, DY), np.complex128)
+    x[0, 2] = wave
+    w = np.zeros((8, 64), np.complex128)
+    w[2, 7] = 1.0
+    y_c = oracle_np.spectral_conv_2d(x, w, x_modes_centered=True)
+    y_0 = oracle_np.spectral_conv_2d(x, w)
+    assert np.abs(y_c[0, 7] - wave).max() < 1e-9
+    assert np.abs(y_0).max() < 1e-9
+    # a positive frequency inside both sets passes both
+    x[0, 2] = np.exp(2j * np.pi * (9 * xx / DX + 3 * yy / DY))
+    assert np.abs(oracle_np.spectral_conv_2d(x, w, x_modes_centered=True) - oracle_np.spectral_conv_2d(x, w)).max() < 1e-9

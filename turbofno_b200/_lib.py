@@ -38,6 +38,7 @@ class Problem(ctypes.Structure):
         ("beta_im", ctypes.c_float),
         ("second_transform_forward", ctypes.c_int),
         ("scale_inverse", ctypes.c_int),
+        ("x_modes_centered", ctypes.c_int),
     ]
 
 

@@ -83,7 +83,8 @@ class SpectralConv:
     """
 
     def __init__(self, rank, bs, DY, K, N, dimX=1, DX=None, variant="D", alpha=1.0 + 0j, beta=0j,
-                 second_transform_forward=False, scale_inverse=True, layout="reference", device=None, modes=64):
+                 second_transform_forward=False, scale_inverse=True, layout="reference", device=None, modes=64,
+                 x_modes_centered=False):
         self.handle = Handle.get(device)
         self.lib = self.handle.lib
         p = Problem()
@@ -95,6 +96,7 @@ class SpectralConv:
         p.alpha_re, p.alpha_im, p.beta_re, p.beta_im = alpha.real, alpha.imag, beta.real, beta.imag
         p.second_transform_forward = int(bool(second_transform_forward))
         p.scale_inverse = int(bool(scale_inverse))
+        p.x_modes_centered = int(bool(x_modes_centered))
         self.rank = rank
         self.B = bs * dimX if rank == 1 else bs
         unit = DY if rank == 1 else p.DX * DY

@@ -101,6 +101,8 @@ int validate(const tfno_problem& p) {
     if (p.rank == 2 && !supported_len(p.DX)) return TFNO_ERR_UNSUPPORTED;
     if (p.K % kSlabK != 0 || p.N % 64 != 0) return TFNO_ERR_UNSUPPORTED;
     if (p.rank == 2 && p.variant == TFNO_VARIANT_D && (p.DX > 256 || p.DY > 256)) return TFNO_ERR_UNSUPPORTED;
+    // centered X modes: the whole-image kernels of the 2D variant D, true inverse only
+    if (p.x_modes_centered && (p.rank != 2 || p.variant != TFNO_VARIANT_D || p.second_transform_forward)) return TFNO_ERR_UNSUPPORTED;
     return TFNO_OK;
 }
 
@@ -377,6 +379,7 @@ int tfno_exec(const tfno_plan* plan, const void* x, const void* w, void* y, void
         ImageParams ii{};  // C -> y
         ii.nimg = p.N * B; ii.per_k = B; ii.in = C; ii.out = yout; ii.stride_b = p.y_stride_b; ii.stride_k = p.y_stride_n;
         ii.gain = f2(scale, 0.f); ii.conj_inverse = conj;
+        fi.centered_x = ii.centered_x = p.x_modes_centered ? 1 : 0;
         ColsParams fc{};   // x -> T1  [K*B][64][DY]
         fc.nimg = p.K * B; fc.per_k = B; fc.DY = p.DY; fc.in = xin; fc.out = T1; fc.stride_b = p.x_stride_b; fc.stride_k = p.x_stride_k;
         ColsParams ic{};   // T2 -> y

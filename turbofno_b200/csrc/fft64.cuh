@@ -230,31 +230,42 @@ TFNO_HD float2 unit_root(int e, int n, float sign) {
 template <int R>
 TFNO_HD constexpr int tw_index(int r, int j) { return ((j >> 1) * R + r) * 2 + (j & 1); }
 
+// `centered`: the kept modes are -32..31 instead of 0..63 (mode k of the result is k - 32 of the
+// signal).  That is the transform of the signal times e^{+2 pi i 32 n / DY}, and for sample
+// n = R*i + r this factor is (-1)^i * e^{+2 pi i 32 r / DY}: a sign on the lane's odd samples,
+// which the 64-point transform applies for free (forward_local), and a constant per lane, which
+// goes into the lane's row of this table.
 template <int R>
-TFNO_HD void fill_forward_table(float2* twF, int tid, int nthreads) {
+TFNO_HD void fill_forward_table(float2* twF, int tid, int nthreads, bool centered = false) {
     constexpr int DY = 64 * R;
     for (int i = tid; i < R * 64; i += nthreads) {
         int r = i >> 6, j = i & 63;
         int k = (j + ((r & (R >> 1)) ? 32 : 0)) & 63;
-        twF[tw_index<R>(r, j)] = unit_root((r * k) & (DY - 1), DY, -1.0f);
+        const int e = centered ? (r * k - 32 * r) & (DY - 1) : (r * k) & (DY - 1);
+        twF[tw_index<R>(r, j)] = unit_root(e, DY, -1.0f);
     }
 }
 
+// `centered` (true inverse only): the 64 given modes are -32..31.  Sample R*j2 + j1 of the result
+// is the ordinary one times e^{-2 pi i 32 (R*j2 + j1) / DY} = (-1)^j2 * e^{-2 pi i 32 j1 / DY}: the
+// constant per lane goes into this table, the sign is a rotation of the transform's input by 32
+// (inverse_pad_lane<CONJ, R, true>).
 template <int R>
-TFNO_HD void fill_inverse_table(float2* twI, int tid, int nthreads, float2 g, bool conj) {
+TFNO_HD void fill_inverse_table(float2* twI, int tid, int nthreads, float2 g, bool conj, bool centered = false) {
     constexpr int DY = 64 * R;
     for (int i = tid; i < R * 64; i += nthreads) {
         int j1 = i >> 6, m = i & 63;
-        twI[tw_index<R>(j1, m)] = cmul(g, unit_root((j1 * m) & (DY - 1), DY, conj ? 1.0f : -1.0f));
+        const int e = centered ? (j1 * m - 32 * j1) & (DY - 1) : (j1 * m) & (DY - 1);
+        twI[tw_index<R>(j1, m)] = cmul(g, unit_root(e, DY, conj ? 1.0f : -1.0f));
     }
 }
 
 // Lane-local part of the forward transform: 64-point transform of the lane's decimated
 // samples (rotated by 32 on the upper half of the group) and the W_DY^{rk} twiddles.
 template <int R>
-TFNO_HD void forward_local(float2 (&v)[64], const float2* __restrict__ twF, int r) {
+TFNO_HD void forward_local(float2 (&v)[64], const float2* __restrict__ twF, int r, bool centered = false) {
     const bool hi = (r & (R >> 1)) != 0;
-    fft64<-1>(v, hi ? -1.0f : 1.0f);
+    fft64<-1>(v, (hi != centered) ? -1.0f : 1.0f);
 #pragma unroll
     for (int j = 0; j < 64; j += 2) {
         float4 t = *reinterpret_cast<const float4*>(twF + tw_index<R>(r, j));
@@ -301,8 +312,8 @@ TFNO_D void exchange_round_top(float2 (&v)[64], int mask) {
 //   twF    : the forward table (fill_forward_table<R>)
 // On return lane r holds modes 64/R*r + j, j < 64/R, in v[slot(j)].
 template <int R>
-TFNO_D void forward_trunc(float2 (&v)[64], const float2* __restrict__ twF, int r) {
-    forward_local<R>(v, twF, r);
+TFNO_D void forward_trunc(float2 (&v)[64], const float2* __restrict__ twF, int r, bool centered = false) {
+    forward_local<R>(v, twF, r, centered);
     // round 1 (partner R/2): slots j<32 keep, slots 32+j go to the partner
     exchange_round_top(v, R >> 1);
     // further rounds: conditional swap so that the kept half sits in the low slots
@@ -315,13 +326,23 @@ TFNO_D void forward_trunc(float2 (&v)[64], const float2* __restrict__ twF, int r
 // Inverse transform by one lane of a group of R: in v[m] = mode m (m<64); out: sample
 // R*j2 + j1 in v[slot(j2)].  twI = the inverse table (fill_inverse_table<R>).
 // CONJ = +1 for a true inverse, -1 for a second forward transform.
-template <int CONJ, int R>
+// ROT32: the result is multiplied by (-1)^j2, done as a rotation of the transform's input by 32
+// (a renaming of registers), for the centered mode set of fill_inverse_table.
+template <int CONJ, int R, bool ROT32 = false>
 TFNO_HD void inverse_pad_lane(float2 (&v)[64], const float2* __restrict__ twI, int j1) {
 #pragma unroll
     for (int m = 0; m < 64; m += 2) {
         float4 t = *reinterpret_cast<const float4*>(twI + tw_index<R>(j1, m));
         v[m] = cmul(v[m], make_float2(t.x, t.y));
         v[m + 1] = cmul(v[m + 1], make_float2(t.z, t.w));
+    }
+    if constexpr (ROT32) {
+#pragma unroll
+        for (int m = 0; m < 32; ++m) {
+            const float2 t = v[m];
+            v[m] = v[m + 32];
+            v[m + 32] = t;
+        }
     }
     fft64<CONJ>(v);
 }

@@ -293,9 +293,12 @@ inline int launch_fft2d_rx(const DeviceInfo& dev, int RY, const ImageParams& p, 
     const bool paired = image_rows_aligned(p, inverse);
 #define TFNO_IMG(RYV)                                                                                                  \
     case RYV:                                                                                                          \
+        if (paired && inverse && p.centered_x)                                                                         \
+            return launch_image<kImageThreads>(dev, ifft2d_pad_kernel<RX, RYV, true, kImageThreads, true>, smem, p, st);  \
         if (paired)                                                                                                    \
             return inverse ? launch_image<kImageThreads>(dev, ifft2d_pad_kernel<RX, RYV, true, kImageThreads>, smem, p, st)   \
                            : launch_image<kImageThreads>(dev, fft2d_trunc_kernel<RX, RYV, true, kImageThreads>, smem, p, st); \
+        if (p.centered_x) return TFNO_ERR_UNSUPPORTED;      /* centered modes only with 16-byte aligned rows */             \
         return inverse ? launch_image<kThreads>(dev, ifft2d_pad_kernel<RX, RYV, false, kThreads>, smem, p, st)         \
                        : launch_image<kThreads>(dev, fft2d_trunc_kernel<RX, RYV, false, kThreads>, smem, p, st);
     switch (RY) { TFNO_IMG(2) TFNO_IMG(4) }

@@ -440,6 +440,7 @@ struct ImageParams {
     long long stride_b, stride_k;      // strides of the full-size side
     float2 gain;
     int conj_inverse;
+    int centered_x;                    // kept X modes are -32..31 (row kx + 32 of the 64 x 64 block) instead of 0..63
 };
 
 // [image][DX][DY] -> [image][64][64]: Y transform of every row (kept modes only) into shared
@@ -459,7 +460,7 @@ __global__ void __launch_bounds__(THREADS, 1) fft2d_trunc_kernel(ImageParams p) 
     float2* twX = twY + RY * 64;                                // [RX][64]
     const int tid = threadIdx.x;
     fill_forward_table<RY>(twY, tid, THREADS);
-    fill_forward_table<RX>(twX, tid, THREADS);
+    fill_forward_table<RX>(twX, tid, THREADS, p.centered_x != 0);
     __syncthreads();
     for (long long img = blockIdx.x; img < p.nimg; img += gridDim.x) {
         const float2* src = p.in + (img % p.per_k) * p.stride_b + (img / p.per_k) * p.stride_k;
@@ -499,7 +500,7 @@ __global__ void __launch_bounds__(THREADS, 1) fft2d_trunc_kernel(ImageParams p) 
                 float2 v[64];
 #pragma unroll
                 for (int n = 0; n < 64; ++n) v[n] = sY[tile_index(RX * n + r, ky)];
-                forward_trunc<RX>(v, twX, r);
+                forward_trunc<RX>(v, twX, r, p.centered_x != 0);
 #pragma unroll
                 for (int j = 0; j < PER; ++j) dst[(PER * r + j) * kModes + ky] = v[slot(j)];
             }
@@ -509,7 +510,7 @@ __global__ void __launch_bounds__(THREADS, 1) fft2d_trunc_kernel(ImageParams p) 
 }
 
 // [image][64][64] -> zero-pad -> inverse along X into shared memory -> inverse along Y -> [image][DX][DY]
-template <int RX, int RY, bool PAIRED, int THREADS>
+template <int RX, int RY, bool PAIRED, int THREADS, bool CENTERED_X = false>
 __global__ void __launch_bounds__(THREADS, 1) ifft2d_pad_kernel(ImageParams p) {
     constexpr int DX = 64 * RX, DY = 64 * RY;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -518,7 +519,7 @@ __global__ void __launch_bounds__(THREADS, 1) ifft2d_pad_kernel(ImageParams p) {
     float2* twX = twY + RY * 64;
     const int tid = threadIdx.x;
     fill_inverse_table<RY>(twY, tid, THREADS, make_float2(1.f, 0.f), p.conj_inverse != 0);
-    fill_inverse_table<RX>(twX, tid, THREADS, p.gain, p.conj_inverse != 0);
+    fill_inverse_table<RX>(twX, tid, THREADS, p.gain, p.conj_inverse != 0, CENTERED_X);
     __syncthreads();
     for (long long img = blockIdx.x; img < p.nimg; img += gridDim.x) {
         const float2* src = p.in + img * (long long)(kModes * kModes);
@@ -533,7 +534,7 @@ __global__ void __launch_bounds__(THREADS, 1) ifft2d_pad_kernel(ImageParams p) {
                 float2 v[64];
 #pragma unroll
                 for (int m = 0; m < 64; ++m) v[m] = __ldg(src + m * kModes + ky);
-                if (p.conj_inverse) inverse_pad_lane<+1, RX>(v, twX, j1);
+                if (p.conj_inverse) inverse_pad_lane<+1, RX, CENTERED_X>(v, twX, j1);
                 else inverse_pad_lane<-1, RX>(v, twX, j1);
 #pragma unroll
                 for (int j2 = 0; j2 < 64; ++j2) sY[tile_index(RX * j2 + j1, ky)] = v[slot(j2)];
