@@ -282,11 +282,19 @@ inline int launch_image(const DeviceInfo& dev, Kernel kernel, size_t smem, const
     int occ = 0;
     int rc = prepare_kernel(kernel, smem, dev, &occ);
     if (rc != TFNO_OK) return rc;
+    if (THREADS != kThreads &&
+        (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, THREADS, smem) != cudaSuccess || occ < 1)) {
+        cudaGetLastError();
+        return TFNO_ERR_CUDA;
+    }
     long long grid = (long long)dev.sms * occ;
     if (grid > p.nimg) grid = p.nimg;
     kernel<<<(unsigned)grid, THREADS, smem, st>>>(p);
     return launch_status();
 }
+// DX = 128: the 64 KB intermediate leaves room for two CTAs per SM if each has 4 warps (255
+// registers per thread); the two then overlap one's X pass (half the warps idle) with the other's Y pass.
+template <int RX> struct ImageThreads { static constexpr int value = (RX == 2) ? 128 : kImageThreads; };
 template <int RX>
 inline int launch_fft2d_rx(const DeviceInfo& dev, int RY, const ImageParams& p, bool inverse, cudaStream_t st) {
     const size_t smem = image_smem_bytes(64 * RX, 64 * RY);
@@ -294,10 +302,10 @@ inline int launch_fft2d_rx(const DeviceInfo& dev, int RY, const ImageParams& p, 
 #define TFNO_IMG(RYV)                                                                                                  \
     case RYV:                                                                                                          \
         if (paired && inverse && p.centered_x)                                                                         \
-            return launch_image<kImageThreads>(dev, ifft2d_pad_kernel<RX, RYV, true, kImageThreads, true>, smem, p, st);  \
+            return launch_image<ImageThreads<RX>::value>(dev, ifft2d_pad_kernel<RX, RYV, true, ImageThreads<RX>::value, true>, smem, p, st);  \
         if (paired)                                                                                                    \
-            return inverse ? launch_image<kImageThreads>(dev, ifft2d_pad_kernel<RX, RYV, true, kImageThreads>, smem, p, st)   \
-                           : launch_image<kImageThreads>(dev, fft2d_trunc_kernel<RX, RYV, true, kImageThreads>, smem, p, st); \
+            return inverse ? launch_image<ImageThreads<RX>::value>(dev, ifft2d_pad_kernel<RX, RYV, true, ImageThreads<RX>::value>, smem, p, st)   \
+                           : launch_image<ImageThreads<RX>::value>(dev, fft2d_trunc_kernel<RX, RYV, true, ImageThreads<RX>::value>, smem, p, st); \
         if (p.centered_x) return TFNO_ERR_UNSUPPORTED;      /* centered modes only with 16-byte aligned rows */             \
         return inverse ? launch_image<kThreads>(dev, ifft2d_pad_kernel<RX, RYV, false, kThreads>, smem, p, st)         \
                        : launch_image<kThreads>(dev, fft2d_trunc_kernel<RX, RYV, false, kThreads>, smem, p, st);
