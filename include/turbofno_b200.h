@@ -40,7 +40,8 @@ typedef enum {
     TFNO_ERR_ALLOC = 4,         /* host or device allocation failed                               */
     TFNO_ERR_LIBRARY = 5,       /* cuFFT / cuBLAS failure (variant E only)                        */
     TFNO_ERR_WORKSPACE = 6,     /* workspace missing or smaller than tfno_workspace_bytes()       */
-    TFNO_ERR_SCRATCH_LIMIT = 7  /* tfno_spectral_conv2d_static: problem exceeds the static scratch */
+    TFNO_ERR_SCRATCH_LIMIT = 7, /* tfno_spectral_conv2d_static: problem exceeds the static scratch */
+    TFNO_ERR_KERNEL_WAIT = 8    /* tfno_exec_host: a kernel-side bounded wait ran out, y incomplete */
 } tfno_status;
 
 /* Fusion variants, named after the reference executables TurboFNO_{1D,2D}_{A..E}
@@ -94,7 +95,9 @@ int tfno_create(tfno_handle** out, int device);
 int tfno_destroy(tfno_handle* h);
 /* Device-side status word of the handle: 0, or the code of the first bounded wait that ran out
  * inside a kernel (the kernel then stops early and its output is incomplete).  Synchronises the
- * device.  The reference has no counterpart: its kernels contain no waits. */
+ * whole device (all streams) before reading.  tfno_exec is asynchronous and cannot report this
+ * itself: callers that need the guarantee read the word after synchronising; tfno_exec_host does
+ * so and returns TFNO_ERR_KERNEL_WAIT.  The reference has no counterpart: its kernels contain no waits. */
 int tfno_device_status(tfno_handle* h, int* out);
 /* Sets the status word back to 0 (after the caller has dealt with a reported time-out). */
 int tfno_device_status_reset(tfno_handle* h);
@@ -128,6 +131,20 @@ int tfno_exec(const tfno_plan* plan, const void* x, const void* w, void* y,
  * per plan).  Replaces the cudaMemcpy + launch sequence at
  * fusion_variants/1D_D_exp_fused_fft_cgemm_ifft/fused.cu:116-128.  Requires the reference layout. */
 int tfno_exec_host(tfno_plan* plan, const void* x_host, const void* w_host, void* y_host);
+
+/* Batch items per pipeline chunk of tfno_exec_host (0 = choose: about 64 MiB of input per chunk,
+ * at least eight chunks per call).  Call before the first tfno_exec_host of the plan.  A tuning
+ * knob with no counterpart in the reference, whose drivers copy the whole input with one
+ * cudaMemcpy (fusion_variants/1D_D_exp_fused_fft_cgemm_ifft/fused.cu:116). */
+int tfno_plan_set_host_chunk(tfno_plan* plan, long long batch_items);
+
+/* Writes the comma-separated names of the kernels (and library calls) one tfno_exec of this plan
+ * launches, in launch order, e.g. "spectral_tc_kernel<4,1>" or
+ * "fft2d_trunc_kernel<4,4,paired,256>,cgemm_tc_kernel<128>,ifft2d_pad_kernel<4,4,paired,256>".
+ * It is produced by a dry run of the dispatch code tfno_exec itself executes.  Stands in for reading
+ * which table entry a reference driver launches
+ * (fusion_variants/1D_D_exp_fused_fft_cgemm_ifft/fused.cu:15-16,126). */
+int tfno_plan_kernels(const tfno_plan* plan, char* buf, size_t cap);
 
 const char* tfno_status_string(int status);
 
@@ -179,13 +196,19 @@ int tfno_ifft_stride(tfno_handle* h, int log2_len, const void* in, void* out, in
  * plug-ins called between another framework's allocator operations, where a cudaMalloc would
  * force a device-wide synchronisation.  It computes one 2D spectral-convolution layer (FNO
  * semantics: alpha * contraction, true inverse, 1/(DX*DY)) in the reference layout
- * x[K][bs][DX][DY], w[k + n*K], y[N][bs][DX][DY], exactly like a variant-D tfno_exec, but takes its
- * two spectrum buffers from a fixed 64 MiB device array inside the library image.  Every GPU that
- * loads the library carries that array until the process exits.
+ * x[K][bs][DX][DY], w[k + n*K], y[N][bs][DX][DY], with the kernel sequence of a variant-D tfno_exec
+ * (image transform, channel contraction, image inverse), but takes its two spectrum buffers from
+ * a fixed 64 MiB device array inside the library image.  Every GPU that loads the library carries
+ * that array until the process exits.  The contraction always runs on the FP32 kernel here (a
+ * plan may pick the tensor-core contraction, which rounds differently in the last bits and is
+ * about three times faster on that step), so results agree with tfno_exec to rounding
+ * (relative L2 difference around 1e-7), not bit for bit.
  *
  *   - no cudaMalloc / cudaFree / allocating library call is made, on any call
  *   - limit: 8*4096*bs*(K + N) bytes (each term rounded up to 256) must fit in
- *     tfno_static_scratch_bytes(); larger problems return TFNO_ERR_SCRATCH_LIMIT and do nothing
+ *     tfno_static_scratch_bytes(); larger problems return TFNO_ERR_SCRATCH_LIMIT, and a K too
+ *     large for the contraction's shared memory returns TFNO_ERR_UNSUPPORTED; a refused call
+ *     enqueues nothing
  *   - DX, DY in {128, 256}; K a multiple of 8, N a multiple of 64; 16-byte aligned pointers
  *   - runs on the CURRENT device, asynchronously on `stream`
  *   - the first call on a device looks up the array's device address and the device limits

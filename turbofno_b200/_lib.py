@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(_PKG, "libturbofno_b200.so")
 OK = 0
 ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_ALLOC, ERR_LIBRARY, ERR_WORKSPACE = 1, 2, 3, 4, 5, 6
 ERR_SCRATCH_LIMIT = 7
+ERR_KERNEL_WAIT = 8
 VARIANT = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
 
 
@@ -57,6 +58,8 @@ SYMBOLS = {
     "tfno_workspace_bytes": (ctypes.c_size_t, [_vp]),
     "tfno_exec": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "tfno_exec_host": (_i, [_vp, _vp, _vp, _vp]),
+    "tfno_plan_set_host_chunk": (_i, [_vp, _ll]),
+    "tfno_plan_kernels": (_i, [_vp, ctypes.c_char_p, ctypes.c_size_t]),
     "tfno_status_string": (ctypes.c_char_p, [_i]),
     "tfno_fused_fft_cgemm_ifft": (_i, [_vp, _i, _ll, _i, _i, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _vp]),
     "tfno_fused_fft_cgemm": (_i, [_vp, _i, _ll, _i, _i, _vp, _vp, _vp, _f, _f, _f, _f, _vp]),

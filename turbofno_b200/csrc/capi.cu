@@ -18,10 +18,11 @@ struct tfno_handle_s {
 struct HostStaging {
     bool ready = false;
     long long chunk_rows = 0;           // batch items per pipeline chunk
+    long long chunk_override = 0;       // set by tfno_plan_set_host_chunk before the first host call
     float2* dx[2] = {nullptr, nullptr};
     float2* dy[2] = {nullptr, nullptr};
     void* dws[2] = {nullptr, nullptr};
-    float2* dw = nullptr;
+    float2* dw[2] = {nullptr, nullptr}; // one copy of the weights per stream: no ordering between the two needed
     cudaStream_t stream[2] = {nullptr, nullptr};
     tfno_plan_s* chunk_plan = nullptr;  // plan for chunk_rows batch items
     tfno_plan_s* tail_plan = nullptr;   // plan for the last, shorter chunk (if any)
@@ -106,6 +107,23 @@ int validate(const tfno_problem& p) {
     return TFNO_OK;
 }
 
+void host_staging_free(HostStaging& hs) {
+    for (int i = 0; i < 2; ++i) {
+        if (hs.dx[i]) cudaFree(hs.dx[i]);
+        if (hs.dy[i]) cudaFree(hs.dy[i]);
+        if (hs.dws[i]) cudaFree(hs.dws[i]);
+        if (hs.dw[i]) cudaFree(hs.dw[i]);
+        if (hs.stream[i]) cudaStreamDestroy(hs.stream[i]);
+        hs.dx[i] = hs.dy[i] = hs.dw[i] = nullptr;
+        hs.dws[i] = nullptr;
+        hs.stream[i] = nullptr;
+    }
+    if (hs.chunk_plan) tfno_plan_destroy(hs.chunk_plan);
+    if (hs.tail_plan) tfno_plan_destroy(hs.tail_plan);
+    hs.chunk_plan = hs.tail_plan = nullptr;
+    hs.ready = false;
+}
+
 }  // namespace
 
 extern "C" {
@@ -120,6 +138,7 @@ const char* tfno_status_string(int status) {
         case TFNO_ERR_LIBRARY: return "cuFFT or cuBLAS call failed";
         case TFNO_ERR_WORKSPACE: return "workspace pointer missing";
         case TFNO_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the library's static 64 MiB array holds";
+        case TFNO_ERR_KERNEL_WAIT: return "a kernel-side wait ran out; the output is incomplete (see tfno_device_status)";
     }
     return "unknown status";
 }
@@ -184,7 +203,9 @@ int tfno_destroy(tfno_handle* h) {
 int tfno_device_status(tfno_handle* h, int* out) {
     if (!h || !out) return TFNO_ERR_INVALID_ARG;
     DeviceGuard guard(h->dev.device);
-    if (!guard.ok || cudaMemcpy(out, h->dev.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    // every stream of the device, non-blocking ones included, before the word is read
+    if (!guard.ok || cudaDeviceSynchronize() != cudaSuccess ||
+        cudaMemcpy(out, h->dev.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
         cudaGetLastError();
         return TFNO_ERR_CUDA;
     }
@@ -236,16 +257,7 @@ int tfno_plan_destroy(tfno_plan* plan) {
     DeviceGuard guard(plan->h->dev.device);
     if (plan->have_fft) { cufftDestroy(plan->fft_fwd); cufftDestroy(plan->fft_inv); }
     if (plan->blas) cublasDestroy(plan->blas);
-    HostStaging& hs = plan->host;
-    for (int i = 0; i < 2; ++i) {
-        if (hs.dx[i]) cudaFree(hs.dx[i]);
-        if (hs.dy[i]) cudaFree(hs.dy[i]);
-        if (hs.dws[i]) cudaFree(hs.dws[i]);
-        if (hs.stream[i]) cudaStreamDestroy(hs.stream[i]);
-    }
-    if (hs.dw) cudaFree(hs.dw);
-    if (hs.chunk_plan) tfno_plan_destroy(hs.chunk_plan);
-    if (hs.tail_plan) tfno_plan_destroy(hs.tail_plan);
+    host_staging_free(plan->host);
     delete plan;
     return TFNO_OK;
 }
@@ -305,14 +317,13 @@ int tfno_plan_create(tfno_handle* h, const tfno_problem* problem, tfno_plan** ou
 
 size_t tfno_workspace_bytes(const tfno_plan* plan) { return plan ? plan->ws_bytes : 0; }
 
-int tfno_exec(const tfno_plan* plan, const void* x, const void* w, void* y, void* workspace, void* stream) {
-    if (!plan || !x || !w || !y) return TFNO_ERR_INVALID_ARG;
-    if (!aligned16(x) || !aligned16(y) || !aligned16(w) || !aligned16(workspace)) return TFNO_ERR_INVALID_ARG;
-    if (plan->ws_bytes > 0 && !workspace) return TFNO_ERR_WORKSPACE;
+}  // extern "C"
+
+// The dispatch of one layer.  With dev.record set it is a dry run: every launcher appends the
+// name of the kernel it would launch and nothing touches the device.
+static int exec_impl(const tfno_plan* plan, const DeviceInfo& dev, const void* x, const void* w, void* y, void* workspace,
+                     void* stream) {
     const tfno_problem& p = plan->p;
-    const DeviceInfo& dev = plan->h->dev;
-    DeviceGuard guard(dev.device);
-    if (!guard.ok) return TFNO_ERR_CUDA;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const Workspace ws = carve(*plan);
     char* wsb = static_cast<char*>(workspace);
@@ -396,6 +407,7 @@ int tfno_exec(const tfno_plan* plan, const void* x, const void* w, void* y, void
                 rc = launch_fft2d(dev, p.DX, p.DY, fi, false, st);
                 if (rc) return rc;
                 t.x = A; t.y = C;
+                t.beta = f2(0.f, 0.f);      // D ignores beta in both ranks (the spectrum buffer C is scratch)
                 rc = launch_tile<false, false>(dev, p.DY, t, st);
                 if (rc) return rc;
                 return launch_fft2d(dev, p.DX, p.DY, ii, true, st);
@@ -438,6 +450,14 @@ int tfno_exec(const tfno_plan* plan, const void* x, const void* w, void* y, void
     // fusion_variants/2D_E_baseline/fused_trunc_2D.cu:238-253, stream-ordered, without the host
     // synchronisation after every step.  The 1/len scale rides on alpha (beta must then be 0 for
     // FNO semantics; with scale_inverse = 0 any beta behaves as in the reference).
+    if (dev.record) {
+        record_launch(dev, "cufftExecC2C");
+        record_launch(dev, p.rank == 1 ? "truncate_rows_kernel" : "truncate_corner_kernel");
+        record_launch(dev, "cublasCgemm");
+        record_launch(dev, p.rank == 1 ? "zero_pad_rows_kernel" : "zero_pad_corner_kernel");
+        record_launch(dev, "cufftExecC2C");
+        return TFNO_OK;
+    }
     if (cufftSetStream(plan->fft_fwd, st) != CUFFT_SUCCESS || cufftSetStream(plan->fft_inv, st) != CUFFT_SUCCESS ||
         cublasSetStream(plan->blas, st) != CUBLAS_STATUS_SUCCESS)
         return TFNO_ERR_LIBRARY;
@@ -467,6 +487,29 @@ int tfno_exec(const tfno_plan* plan, const void* x, const void* w, void* y, void
     return TFNO_OK;
 }
 
+extern "C" {
+
+int tfno_exec(const tfno_plan* plan, const void* x, const void* w, void* y, void* workspace, void* stream) {
+    if (!plan || !x || !w || !y) return TFNO_ERR_INVALID_ARG;
+    if (!aligned16(x) || !aligned16(y) || !aligned16(w) || !aligned16(workspace)) return TFNO_ERR_INVALID_ARG;
+    if (plan->ws_bytes > 0 && !workspace) return TFNO_ERR_WORKSPACE;
+    const DeviceInfo& dev = plan->h->dev;
+    DeviceGuard guard(dev.device);
+    if (!guard.ok) return TFNO_ERR_CUDA;
+    return exec_impl(plan, dev, x, w, y, workspace, stream);
+}
+
+int tfno_plan_kernels(const tfno_plan* plan, char* buf, size_t cap) {
+    if (!plan || !buf || cap < 2) return TFNO_ERR_INVALID_ARG;
+    buf[0] = 0;
+    DeviceInfo dev = plan->h->dev;
+    dev.record = buf;
+    dev.record_cap = cap;
+    // dry run over stand-in operands: 256-byte aligned, never dereferenced
+    char* fake = reinterpret_cast<char*>(static_cast<uintptr_t>(1) << 20);
+    return exec_impl(plan, dev, fake, fake, fake, fake, nullptr);
+}
+
 // ------------------------------------------------------------------------------------------------
 // Host-buffer execution: batch chunks pipelined over two streams (copy-in, layer, copy-out each
 // stream-ordered; the two streams overlap one another's copies and kernels).
@@ -476,8 +519,12 @@ static int host_staging_init(tfno_plan_s* plan) {
     if (hs.ready) return TFNO_OK;
     const tfno_problem& p = plan->p;
     const long long unit = (p.rank == 1) ? (long long)p.dimX * p.DY : image_elems(p);   // elements per batch item and channel
-    // aim at ~64 MiB of input per chunk, at least 1 batch item, at most the whole batch
+    // Chunk size: about 64 MiB of input, but at least eight chunks per call when the batch allows
+    // it, so that copy-in, layer and copy-out of neighbouring chunks overlap on the two streams
+    // also for a small batch (a shard of a multi-GPU job).
     long long chunk = (64LL << 20) / (long long)(sizeof(float2) * unit * p.K);
+    if (chunk > (p.bs + 7) / 8) chunk = (p.bs + 7) / 8;
+    if (hs.chunk_override > 0) chunk = hs.chunk_override;
     if (chunk < 1) chunk = 1;
     if (chunk > p.bs) chunk = p.bs;
     hs.chunk_rows = chunk;
@@ -486,24 +533,35 @@ static int host_staging_init(tfno_plan_s* plan) {
     cp.bs = chunk;
     cp.x_stride_b = cp.x_stride_k = cp.y_stride_b = cp.y_stride_n = 0;
     int rc = tfno_plan_create(plan->h, &cp, &hs.chunk_plan);
-    if (rc) return rc;
-    if (hs.tail_rows) {
+    if (rc == TFNO_OK && hs.tail_rows) {
         cp.bs = hs.tail_rows;
         rc = tfno_plan_create(plan->h, &cp, &hs.tail_plan);
-        if (rc) return rc;
     }
-    const size_t xin = sizeof(float2) * (size_t)(unit * p.K * chunk), yout = sizeof(float2) * (size_t)(unit * p.N * chunk);
-    const size_t wsz = hs.chunk_plan->ws_bytes;
-    for (int i = 0; i < 2; ++i) {
-        if (cudaMalloc(&hs.dx[i], xin) != cudaSuccess || cudaMalloc(&hs.dy[i], yout) != cudaSuccess ||
-            (wsz && cudaMalloc(&hs.dws[i], wsz) != cudaSuccess) ||
-            cudaStreamCreateWithFlags(&hs.stream[i], cudaStreamNonBlocking) != cudaSuccess) {
-            cudaGetLastError();
-            return TFNO_ERR_ALLOC;
+    if (rc == TFNO_OK) {
+        const size_t xin = sizeof(float2) * (size_t)(unit * p.K * chunk), yout = sizeof(float2) * (size_t)(unit * p.N * chunk);
+        const size_t wsz = hs.chunk_plan->ws_bytes;
+        for (int i = 0; i < 2 && rc == TFNO_OK; ++i) {
+            if (cudaMalloc(&hs.dx[i], xin) != cudaSuccess || cudaMalloc(&hs.dy[i], yout) != cudaSuccess ||
+                (wsz && cudaMalloc(&hs.dws[i], wsz) != cudaSuccess) ||
+                cudaMalloc(&hs.dw[i], sizeof(float2) * (size_t)p.K * p.N) != cudaSuccess ||
+                cudaStreamCreateWithFlags(&hs.stream[i], cudaStreamNonBlocking) != cudaSuccess) {
+                cudaGetLastError();
+                rc = TFNO_ERR_ALLOC;
+            }
         }
     }
-    if (cudaMalloc(&hs.dw, sizeof(float2) * (size_t)p.K * p.N) != cudaSuccess) { cudaGetLastError(); return TFNO_ERR_ALLOC; }
+    if (rc != TFNO_OK) {
+        host_staging_free(hs);          // nothing half-built survives a failed set-up
+        return rc;
+    }
     hs.ready = true;
+    return TFNO_OK;
+}
+
+int tfno_plan_set_host_chunk(tfno_plan* plan, long long batch_items) {
+    if (!plan || batch_items < 0) return TFNO_ERR_INVALID_ARG;
+    if (plan->host.ready) return TFNO_ERR_INVALID_ARG;      // staging already sized
+    plan->host.chunk_override = batch_items;
     return TFNO_OK;
 }
 
@@ -518,36 +576,48 @@ int tfno_exec_host(tfno_plan* plan, const void* x_host, const void* w_host, void
     const tfno_problem& p = plan->p;
     const long long unit = (p.rank == 1) ? (long long)p.dimX * p.DY : image_elems(p);
     const size_t full_pitch = sizeof(float2) * (size_t)(unit * p.bs);   // bytes between channels on the host
-    if (cudaMemcpyAsync(hs.dw, w_host, sizeof(float2) * (size_t)p.K * p.N, cudaMemcpyHostToDevice, hs.stream[0]) != cudaSuccess ||
-        cudaStreamSynchronize(hs.stream[0]) != cudaSuccess) {
+    // On any failure: wait for what is already in flight (the copies read and write caller-owned
+    // host buffers) before returning.
+    auto fail = [&](int code) {
+        cudaStreamSynchronize(hs.stream[0]);
+        cudaStreamSynchronize(hs.stream[1]);
         cudaGetLastError();
-        return TFNO_ERR_CUDA;
-    }
+        return code;
+    };
     int slot = 0;
-    for (long long b0 = 0; b0 < p.bs; b0 += hs.chunk_rows, slot ^= 1) {
+    long long chunk_index = 0;
+    for (long long b0 = 0; b0 < p.bs; b0 += hs.chunk_rows, slot ^= 1, ++chunk_index) {
         const long long nb = (p.bs - b0 < hs.chunk_rows) ? p.bs - b0 : hs.chunk_rows;
         tfno_plan_s* cp = (nb == hs.chunk_rows) ? hs.chunk_plan : hs.tail_plan;
         const size_t width = sizeof(float2) * (size_t)(unit * nb);
         cudaStream_t st = hs.stream[slot];
+        // each stream brings its own copy of the weights with its first chunk (stream-ordered
+        // before that chunk's kernels; no host synchronisation, no ordering between the streams)
+        if (chunk_index < 2 &&
+            cudaMemcpyAsync(hs.dw[slot], w_host, sizeof(float2) * (size_t)p.K * p.N, cudaMemcpyHostToDevice, st) != cudaSuccess)
+            return fail(TFNO_ERR_CUDA);
         // [K][bs][unit] on the host -> compact [K][nb][unit] on the device
         if (cudaMemcpy2DAsync(hs.dx[slot], width, static_cast<const char*>(x_host) + sizeof(float2) * (size_t)(unit * b0),
-                              full_pitch, width, (size_t)p.K, cudaMemcpyHostToDevice, st) != cudaSuccess) {
-            cudaGetLastError();
-            return TFNO_ERR_CUDA;
-        }
-        rc = tfno_exec(cp, hs.dx[slot], hs.dw, hs.dy[slot], hs.dws[slot], st);
-        if (rc) return rc;
+                              full_pitch, width, (size_t)p.K, cudaMemcpyHostToDevice, st) != cudaSuccess)
+            return fail(TFNO_ERR_CUDA);
+        rc = tfno_exec(cp, hs.dx[slot], hs.dw[slot], hs.dy[slot], hs.dws[slot], st);
+        if (rc) return fail(rc);
         if (cudaMemcpy2DAsync(static_cast<char*>(y_host) + sizeof(float2) * (size_t)(unit * b0), full_pitch, hs.dy[slot], width,
-                              width, (size_t)p.N, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
-            cudaGetLastError();
-            return TFNO_ERR_CUDA;
-        }
+                              width, (size_t)p.N, cudaMemcpyDeviceToHost, st) != cudaSuccess)
+            return fail(TFNO_ERR_CUDA);
     }
     if (cudaStreamSynchronize(hs.stream[0]) != cudaSuccess || cudaStreamSynchronize(hs.stream[1]) != cudaSuccess) {
         cudaGetLastError();
         return TFNO_ERR_CUDA;
     }
-    return TFNO_OK;
+    // y is complete only if no kernel-side wait ran out
+    int word = 0;
+    if (plan->h->dev.status &&
+        cudaMemcpy(&word, plan->h->dev.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return TFNO_ERR_CUDA;
+    }
+    return word == 0 ? TFNO_OK : TFNO_ERR_KERNEL_WAIT;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -738,22 +808,33 @@ int tfno_spectral_conv2d_static(long long bs, int DX, int DY, int K, int N, cons
     if (!x || !w || !y || bs <= 0 || K <= 0 || N <= 0) return TFNO_ERR_INVALID_ARG;
     if (!aligned16(x) || !aligned16(w) || !aligned16(y)) return TFNO_ERR_INVALID_ARG;
     if ((DX != 128 && DX != 256) || (DY != 128 && DY != 256) || K % kSlabK != 0 || N % 64 != 0) return TFNO_ERR_UNSUPPORTED;
-    const size_t spec_in = align_up(sizeof(float2) * (size_t)K * (size_t)bs * kModes * kModes);
-    const size_t spec_out = align_up(sizeof(float2) * (size_t)N * (size_t)bs * kModes * kModes);
+    // size check by division: no product of caller-given sizes is formed before it is known to fit
+    constexpr size_t kPerChannelImage = sizeof(float2) * (size_t)kModes * kModes;      // 32 KiB of spectrum
+    const size_t max_units = kStaticScratchBytes / kPerChannelImage;                     // (K + N) * bs may not exceed this
+    if ((size_t)K > max_units || (size_t)N > max_units || (size_t)bs > max_units / ((size_t)K + (size_t)N))
+        return TFNO_ERR_SCRATCH_LIMIT;
+    const size_t spec_in = align_up(kPerChannelImage * (size_t)K * (size_t)bs);
+    const size_t spec_out = align_up(kPerChannelImage * (size_t)N * (size_t)bs);
     if (spec_in + spec_out > kStaticScratchBytes) return TFNO_ERR_SCRATCH_LIMIT;
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess) { cudaGetLastError(); return TFNO_ERR_CUDA; }
     StaticDevice* sd = nullptr;
     int rc = static_device_setup(device, &sd);
     if (rc != TFNO_OK) return rc;
+    // every launch of this call must fit before the first one is enqueued: a refused call does nothing
+    if ((long long)image_smem_bytes(DX, DY) > sd->dev.max_smem_optin ||
+        (long long)tile_smem_bytes(2, false, false, K, N > 128 ? 128 : N) > sd->dev.max_smem_optin)
+        return TFNO_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     float2* S = reinterpret_cast<float2*>(sd->scratch);
     float2* C = reinterpret_cast<float2*>(sd->scratch + spec_in);
     const long long img = (long long)DX * DY;
 
-    // image transform, channel contraction, image inverse: the same three kernels tfno_exec runs
-    // for a 2D variant-D plan.  Every scratch element that is read has been written by the
-    // preceding kernel of this call (beta = 0), so nothing has to start at zero.
+    // image transform, channel contraction, image inverse: the kernel sequence of a 2D variant-D
+    // plan, except that the contraction always runs on the FP32 row-tile kernel (the tensor-core
+    // contraction reports through a handle's status word, and this entry point has no handle).
+    // Every scratch element that is read has been written by the preceding kernel of this call
+    // (beta = 0), so nothing has to start at zero.
     ImageParams fi{};
     fi.nimg = K * bs; fi.per_k = bs; fi.in = static_cast<const float2*>(x); fi.out = S; fi.stride_b = img; fi.stride_k = bs * img;
     rc = launch_fft2d(sd->dev, DX, DY, fi, false, st);

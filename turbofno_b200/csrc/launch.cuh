@@ -3,6 +3,11 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cstdio>
+#include <cstring>
+#include <mutex>
+#ifdef TFNO_TC_TRACE
+#include <vector>
+#endif
 #include "../../include/turbofno_b200.h"
 #include "spectral_kernels.cuh"
 #include "spectral_tc.cuh"
@@ -16,6 +21,11 @@ struct DeviceInfo {
     int max_smem_optin = 0;
     bool use_tensor_cores = true;   // tcgen05 fused kernel where its shape limits allow
     int* status = nullptr;          // device word written by kernels whose bounded waits ran out
+    // Dry run: when set, every launcher appends the name of the kernel it would launch (comma
+    // separated) and launches nothing.  tfno_plan_kernels reports a plan's kernels this way, from
+    // the same dispatch code tfno_exec runs.
+    char* record = nullptr;
+    size_t record_cap = 0;
 };
 
 inline int log2_exact(long long v) {
@@ -25,23 +35,83 @@ inline int log2_exact(long long v) {
 }
 inline bool supported_len(int len) { return len == 128 || len == 256 || len == 512 || len == 1024; }
 
-template <typename Kernel>
-inline int prepare_kernel(Kernel kernel, size_t smem, const DeviceInfo& dev, int* blocks_per_sm) {
+// Appends "name" (printf-style) to the record buffer; true when the caller is a dry run.
+inline bool record_launch(const DeviceInfo& dev, const char* fmt, int a = 0, int b = 0, int c = 0, int d = 0) {
+    if (!dev.record) return false;
+    const size_t used = std::strlen(dev.record);
+    if (used + 2 < dev.record_cap) {
+        int n = 0;
+        if (used) n = std::snprintf(dev.record + used, dev.record_cap - used, ",");
+        std::snprintf(dev.record + used + n, dev.record_cap - used - n, fmt, a, b, c, d);
+    }
+    return true;
+}
+
+// Per-kernel launch set-up, done once per (kernel, device, block size, shared-memory size) and
+// remembered: the opt-in to more than 48 KB of dynamic shared memory and the resident blocks per
+// SM.  A fixed table, no heap: the allocation-free entry point goes through here too.
+struct KernelSetupEntry {
+    const void* func;
+    int device, threads;
+    size_t smem;
+    int occ;
+};
+constexpr int kKernelSetupSlots = 512;
+inline KernelSetupEntry* kernel_setup_table() {
+    static KernelSetupEntry table[kKernelSetupSlots];
+    return table;
+}
+inline std::mutex& kernel_setup_mutex() {
+    static std::mutex m;
+    return m;
+}
+inline int kernel_setup_count(int add = 0) {
+    static int n = 0;
+    n += add;
+    return n;
+}
+
+inline int prepare_kernel_cached(const void* func, int threads, size_t smem, const DeviceInfo& dev, int* blocks_per_sm) {
     if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
-    if (smem > 48 * 1024) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    std::lock_guard<std::mutex> lock(kernel_setup_mutex());
+    KernelSetupEntry* table = kernel_setup_table();
+    const int n = kernel_setup_count();
+    size_t opted_in = 48 * 1024;        // largest dynamic shared-memory size this kernel has been opted in to so far
+    for (int i = 0; i < n; ++i) {
+        if (table[i].func != func || table[i].device != dev.device) continue;
+        if (table[i].threads == threads && table[i].smem == smem) {
+            *blocks_per_sm = table[i].occ;
+            return TFNO_OK;
+        }
+        if (table[i].smem > opted_in) opted_in = table[i].smem;
+    }
+    // the attribute is one value per kernel: only ever raise it, or a launch that was set up
+    // earlier with a larger size would be refused
+    if (smem > opted_in) {
+        if (cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
             cudaGetLastError();
             return TFNO_ERR_CUDA;
         }
     }
     int occ = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kThreads, smem) != cudaSuccess || occ < 1) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, func, threads, smem) != cudaSuccess || occ < 1) {
         cudaGetLastError();
         return TFNO_ERR_CUDA;
+    }
+    if (n < kKernelSetupSlots) {
+        table[n] = KernelSetupEntry{func, dev.device, threads, smem, occ};
+        kernel_setup_count(1);
     }
     *blocks_per_sm = occ;
     return TFNO_OK;
 }
+
+template <typename Kernel>
+inline int prepare_kernel(Kernel kernel, size_t smem, const DeviceInfo& dev, int* blocks_per_sm, int threads = kThreads) {
+    return prepare_kernel_cached(reinterpret_cast<const void*>(kernel), threads, smem, dev, blocks_per_sm);
+}
+
+#include "tc_trace.cuh"
 
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? TFNO_OK : TFNO_ERR_CUDA; }
 
@@ -55,6 +125,8 @@ template <int R, bool FWD, bool INV, int NB>
 inline int launch_tile_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
     auto kernel = spectral_tile_kernel<R, FWD, INV, NB>;
     size_t smem = tile_smem_bytes(R, FWD, INV, p.K, p.N);
+    if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
+    if (record_launch(dev, "spectral_tile_kernel<%d,%d,%d,%d>", R, FWD, INV, NB)) return TFNO_OK;
     int occ = 0;
     int rc = prepare_kernel(kernel, smem, dev, &occ);
     if (rc != TFNO_OK) return rc;
@@ -75,21 +147,16 @@ inline int launch_tile_r(const DeviceInfo& dev, int R, const TileParams& p, cuda
     return TFNO_ERR_UNSUPPORTED;
 }
 
-// Tensor-core fused kernel: N a multiple of 64 (64 per launch), K a multiple of the chunk size (64/R channels) up to 64,
-// transform length 128 or 256.
+// Tensor-core fused kernel: N a multiple of 64 (64 per launch), K a multiple of the chunk size
+// (16 channels at DY = 256, 32 at DY = 128) up to 96 (tensor memory holds the weights, 4K columns,
+// next to two accumulators), transform length 128 or 256.
 inline bool tc_eligible(const DeviceInfo& dev, int len, const TileParams& p) {
     if (!dev.use_tensor_cores || !dev.status) return false;
     if (p.N % 64 != 0 || (len != 128 && len != 256)) return false;
     // N > 64 takes one launch per 64 output channels: worth it only when the launches are long
     if (p.N > 64 && p.rows < 2LL * dev.sms) return false;
-    const int CH = 64 / (len / 64);
-    if (p.K < CH || p.K > 64 || p.K % CH != 0) return false;
-    // With an odd number (> 1) of chunks per row the two ring stages alternate between the two
-    // forward half-teams, and a half-team would wait on a barrier whose previous phase it has not
-    // seen (a parity wait cannot tell "not yet" from "two phases on"): those shapes (K = 48 at
-    // DY = 256) take the FP32 kernel.
-    const int NC = p.K / CH;
-    return NC == 1 || NC % 2 == 0;
+    const int CH = 128 / (len / 32);
+    return p.K >= CH && p.K <= 96 && p.K % CH == 0;
 }
 
 template <int R, bool INVERSE>
@@ -97,9 +164,21 @@ inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream
     auto kernel = tc::spectral_tc_kernel<R, INVERSE>;
     const size_t smem = tc::tc_smem_bytes<R>(p.K);
     if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        cudaGetLastError();
-        return TFNO_ERR_CUDA;
+    if (record_launch(dev, "spectral_tc_kernel<%d,%d>", R, INVERSE)) return TFNO_OK;
+    int occ = 0;
+    int rc = prepare_kernel(kernel, smem, dev, &occ, tc::kTcThreads);
+    if (rc != TFNO_OK) return rc;
+    {
+        // The kernel redistributes registers between its warpgroups (setmaxnreg); the CTA's pool is
+        // what it was launched with.  Refuse to launch a build whose pool is too small instead of
+        // letting the register increase wait for ever.
+        static int pool_ok = -1;
+        if (pool_ok < 0) {
+            cudaFuncAttributes fa{};
+            pool_ok = (cudaFuncGetAttributes(&fa, kernel) == cudaSuccess &&
+                       fa.numRegs * tc::kTcThreads >= 512 * tc::kComputeRegs + 256 * tc::kHelperRegs) ? 1 : 0;
+        }
+        if (!pool_ok) return TFNO_ERR_UNSUPPORTED;
     }
     tc::TcParams q{};
     q.rows = p.rows; q.K = p.K;
@@ -110,24 +189,11 @@ inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream
     long long grid = dev.sms;
     if (grid > p.rows) grid = p.rows;
 #ifdef TFNO_TC_TRACE
-    static long long* trace_buf = nullptr;
-    if (!trace_buf) cudaMalloc(&trace_buf, sizeof(long long) * 148 * 16 * 12);
-    cudaMemset(trace_buf, 0, sizeof(long long) * 148 * 16 * 12);
-    q.trace = trace_buf;
+    q.trace = tc_trace_buffer(dev, true);
 #endif
     kernel<<<(unsigned)grid, tc::kTcThreads, smem, st>>>(q);
 #ifdef TFNO_TC_TRACE
-    {
-        cudaDeviceSynchronize();
-        static long long host[148 * 16 * 12];
-        cudaMemcpy(host, trace_buf, sizeof(host), cudaMemcpyDeviceToHost);
-        const char* role[14] = {"F0", "I1", "F2", "I3", "F4", "I5", "F6", "I7", "X8", "X9", "X10", "X11", "PROD", "MMA"};
-        for (int w = 0; w < 14; ++w) {
-            double t[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-            for (int b = 0; b < (int)grid; ++b) for (int k = 0; k < 12; ++k) t[k] += (double)host[(b * 16 + w) * 12 + k] / grid;
-            fprintf(stderr, "trace %-4s total=%8.0f w0=%7.0f w1=%7.0f w2=%7.0f w3=%7.0f load=%7.0f mma=%7.0f fft=%7.0f in=%7.0f mid=%7.0f out=%7.0f loop=%7.0f\n", role[w], t[0], t[1], t[2], t[3], t[4], t[5], t[6], t[7], t[8], t[9], t[10], t[11]);
-        }
-    }
+    tc_trace_report(dev, (int)grid);
 #endif
     return launch_status();
 }
@@ -144,10 +210,10 @@ inline int launch_cgemm_tc_inst(const DeviceInfo& dev, const TileParams& p, cuda
     auto kernel = tcg::cgemm_tc_kernel<TN>;
     const size_t smem = tcg::cgemm_tc_smem_bytes<TN>();
     if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        cudaGetLastError();
-        return TFNO_ERR_CUDA;
-    }
+    if (record_launch(dev, "cgemm_tc_kernel<%d>", TN)) return TFNO_OK;
+    int occ = 0;
+    int rc = prepare_kernel(kernel, smem, dev, &occ, tcg::kGemmThreads);
+    if (rc != TFNO_OK) return rc;
     const long long M = p.rows * kModes;
     tcg::CgemmTcParams q{};
     q.tiles = M / TN; q.K = p.K;
@@ -185,8 +251,8 @@ inline int launch_tile(const DeviceInfo& dev, int len, TileParams p, cudaStream_
                 q.w = p.w + (long long)n0 * p.w_stride_n;
                 q.y = p.y + (long long)n0 * p.y_stride_n;
                 int rc;
-                if (q.conj_inverse) rc = len == 128 ? launch_tc_inst<2, true>(dev, q, st) : launch_tc_inst<4, true>(dev, q, st);
-                else rc = len == 128 ? launch_tc_inst<2, false>(dev, q, st) : launch_tc_inst<4, false>(dev, q, st);
+                if (q.conj_inverse) rc = len == 128 ? launch_tc_inst<4, true>(dev, q, st) : launch_tc_inst<8, true>(dev, q, st);
+                else rc = len == 128 ? launch_tc_inst<4, false>(dev, q, st) : launch_tc_inst<8, false>(dev, q, st);
                 if (rc != TFNO_OK) return rc;
             }
             return TFNO_OK;
@@ -210,8 +276,9 @@ inline int launch_tile(const DeviceInfo& dev, int len, TileParams p, cudaStream_
 
 template <typename Params, typename Kernel>
 inline int launch_persistent(const DeviceInfo& dev, Kernel kernel, size_t smem, long long work_blocks,
-                             const Params& p, cudaStream_t st) {
+                             const Params& p, cudaStream_t st, const char* name, int R) {
     if (work_blocks <= 0) return TFNO_OK;
+    if (record_launch(dev, name, R)) return TFNO_OK;
     int occ = 0;
     int rc = prepare_kernel(kernel, smem, dev, &occ);
     if (rc != TFNO_OK) return rc;
@@ -225,10 +292,10 @@ inline int launch_fft_rows(const DeviceInfo& dev, int len, const RowsParams& p, 
     const int R = len / 64;
     const long long blocks = (p.nsig + kThreads / R - 1) / (kThreads / R);
     switch (R) {
-        case 2: return launch_persistent(dev, fft_rows_trunc_kernel<2>, 0, blocks, p, st);
-        case 4: return launch_persistent(dev, fft_rows_trunc_kernel<4>, 0, blocks, p, st);
-        case 8: return launch_persistent(dev, fft_rows_trunc_kernel<8>, 0, blocks, p, st);
-        case 16: return launch_persistent(dev, fft_rows_trunc_kernel<16>, 0, blocks, p, st);
+        case 2: return launch_persistent(dev, fft_rows_trunc_kernel<2>, 0, blocks, p, st, "fft_rows_trunc_kernel<%d>", 2);
+        case 4: return launch_persistent(dev, fft_rows_trunc_kernel<4>, 0, blocks, p, st, "fft_rows_trunc_kernel<%d>", 4);
+        case 8: return launch_persistent(dev, fft_rows_trunc_kernel<8>, 0, blocks, p, st, "fft_rows_trunc_kernel<%d>", 8);
+        case 16: return launch_persistent(dev, fft_rows_trunc_kernel<16>, 0, blocks, p, st, "fft_rows_trunc_kernel<%d>", 16);
     }
     return TFNO_ERR_UNSUPPORTED;
 }
@@ -236,10 +303,10 @@ inline int launch_ifft_rows(const DeviceInfo& dev, int len, const RowsParams& p,
     const int R = len / 64;
     const long long blocks = (p.nsig + kThreads / R - 1) / (kThreads / R);
     switch (R) {
-        case 2: return launch_persistent(dev, ifft_rows_pad_kernel<2>, 0, blocks, p, st);
-        case 4: return launch_persistent(dev, ifft_rows_pad_kernel<4>, 0, blocks, p, st);
-        case 8: return launch_persistent(dev, ifft_rows_pad_kernel<8>, 0, blocks, p, st);
-        case 16: return launch_persistent(dev, ifft_rows_pad_kernel<16>, 0, blocks, p, st);
+        case 2: return launch_persistent(dev, ifft_rows_pad_kernel<2>, 0, blocks, p, st, "ifft_rows_pad_kernel<%d>", 2);
+        case 4: return launch_persistent(dev, ifft_rows_pad_kernel<4>, 0, blocks, p, st, "ifft_rows_pad_kernel<%d>", 4);
+        case 8: return launch_persistent(dev, ifft_rows_pad_kernel<8>, 0, blocks, p, st, "ifft_rows_pad_kernel<%d>", 8);
+        case 16: return launch_persistent(dev, ifft_rows_pad_kernel<16>, 0, blocks, p, st, "ifft_rows_pad_kernel<%d>", 16);
     }
     return TFNO_ERR_UNSUPPORTED;
 }
@@ -247,10 +314,10 @@ inline int launch_fft_cols(const DeviceInfo& dev, int len, const ColsParams& p, 
     const int R = len / 64;
     const long long blocks = (p.nimg * p.DY + kThreads / R - 1) / (kThreads / R);
     switch (R) {
-        case 2: return launch_persistent(dev, fft_cols_trunc_kernel<2>, 0, blocks, p, st);
-        case 4: return launch_persistent(dev, fft_cols_trunc_kernel<4>, 0, blocks, p, st);
-        case 8: return launch_persistent(dev, fft_cols_trunc_kernel<8>, 0, blocks, p, st);
-        case 16: return launch_persistent(dev, fft_cols_trunc_kernel<16>, 0, blocks, p, st);
+        case 2: return launch_persistent(dev, fft_cols_trunc_kernel<2>, 0, blocks, p, st, "fft_cols_trunc_kernel<%d>", 2);
+        case 4: return launch_persistent(dev, fft_cols_trunc_kernel<4>, 0, blocks, p, st, "fft_cols_trunc_kernel<%d>", 4);
+        case 8: return launch_persistent(dev, fft_cols_trunc_kernel<8>, 0, blocks, p, st, "fft_cols_trunc_kernel<%d>", 8);
+        case 16: return launch_persistent(dev, fft_cols_trunc_kernel<16>, 0, blocks, p, st, "fft_cols_trunc_kernel<%d>", 16);
     }
     return TFNO_ERR_UNSUPPORTED;
 }
@@ -258,10 +325,10 @@ inline int launch_ifft_cols(const DeviceInfo& dev, int len, const ColsParams& p,
     const int R = len / 64;
     const long long blocks = (p.nimg * p.DY + kThreads / R - 1) / (kThreads / R);
     switch (R) {
-        case 2: return launch_persistent(dev, ifft_cols_pad_kernel<2>, 0, blocks, p, st);
-        case 4: return launch_persistent(dev, ifft_cols_pad_kernel<4>, 0, blocks, p, st);
-        case 8: return launch_persistent(dev, ifft_cols_pad_kernel<8>, 0, blocks, p, st);
-        case 16: return launch_persistent(dev, ifft_cols_pad_kernel<16>, 0, blocks, p, st);
+        case 2: return launch_persistent(dev, ifft_cols_pad_kernel<2>, 0, blocks, p, st, "ifft_cols_pad_kernel<%d>", 2);
+        case 4: return launch_persistent(dev, ifft_cols_pad_kernel<4>, 0, blocks, p, st, "ifft_cols_pad_kernel<%d>", 4);
+        case 8: return launch_persistent(dev, ifft_cols_pad_kernel<8>, 0, blocks, p, st, "ifft_cols_pad_kernel<%d>", 8);
+        case 16: return launch_persistent(dev, ifft_cols_pad_kernel<16>, 0, blocks, p, st, "ifft_cols_pad_kernel<%d>", 16);
     }
     return TFNO_ERR_UNSUPPORTED;
 }
@@ -278,15 +345,13 @@ inline bool image_rows_aligned(const ImageParams& p, bool inverse) {
 // slower (2D layer bs=64, K=N=64, 256x256: 1.21 against 1.10 ms)
 constexpr int kImageThreads = 256;
 template <int THREADS, typename Kernel>
-inline int launch_image(const DeviceInfo& dev, Kernel kernel, size_t smem, const ImageParams& p, cudaStream_t st) {
+inline int launch_image(const DeviceInfo& dev, Kernel kernel, size_t smem, const ImageParams& p, cudaStream_t st,
+                        const char* name, int RX, int RY) {
+    if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
+    if (record_launch(dev, name, RX, RY, THREADS)) return TFNO_OK;
     int occ = 0;
-    int rc = prepare_kernel(kernel, smem, dev, &occ);
+    int rc = prepare_kernel(kernel, smem, dev, &occ, THREADS);
     if (rc != TFNO_OK) return rc;
-    if (THREADS != kThreads &&
-        (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, THREADS, smem) != cudaSuccess || occ < 1)) {
-        cudaGetLastError();
-        return TFNO_ERR_CUDA;
-    }
     long long grid = (long long)dev.sms * occ;
     if (grid > p.nimg) grid = p.nimg;
     kernel<<<(unsigned)grid, THREADS, smem, st>>>(p);
@@ -302,13 +367,13 @@ inline int launch_fft2d_rx(const DeviceInfo& dev, int RY, const ImageParams& p, 
 #define TFNO_IMG(RYV)                                                                                                  \
     case RYV:                                                                                                          \
         if (paired && inverse && p.centered_x)                                                                         \
-            return launch_image<ImageThreads<RX>::value>(dev, ifft2d_pad_kernel<RX, RYV, true, ImageThreads<RX>::value, true>, smem, p, st);  \
+            return launch_image<ImageThreads<RX>::value>(dev, ifft2d_pad_kernel<RX, RYV, true, ImageThreads<RX>::value, true>, smem, p, st, "ifft2d_pad_kernel<%d,%d,paired,%d,centered>", RX, RYV);  \
         if (paired)                                                                                                    \
-            return inverse ? launch_image<ImageThreads<RX>::value>(dev, ifft2d_pad_kernel<RX, RYV, true, ImageThreads<RX>::value>, smem, p, st)   \
-                           : launch_image<ImageThreads<RX>::value>(dev, fft2d_trunc_kernel<RX, RYV, true, ImageThreads<RX>::value>, smem, p, st); \
+            return inverse ? launch_image<ImageThreads<RX>::value>(dev, ifft2d_pad_kernel<RX, RYV, true, ImageThreads<RX>::value>, smem, p, st, "ifft2d_pad_kernel<%d,%d,paired,%d>", RX, RYV)   \
+                           : launch_image<ImageThreads<RX>::value>(dev, fft2d_trunc_kernel<RX, RYV, true, ImageThreads<RX>::value>, smem, p, st, "fft2d_trunc_kernel<%d,%d,paired,%d>", RX, RYV); \
         if (p.centered_x) return TFNO_ERR_UNSUPPORTED;      /* centered modes only with 16-byte aligned rows */             \
-        return inverse ? launch_image<kThreads>(dev, ifft2d_pad_kernel<RX, RYV, false, kThreads>, smem, p, st)         \
-                       : launch_image<kThreads>(dev, fft2d_trunc_kernel<RX, RYV, false, kThreads>, smem, p, st);
+        return inverse ? launch_image<kThreads>(dev, ifft2d_pad_kernel<RX, RYV, false, kThreads>, smem, p, st, "ifft2d_pad_kernel<%d,%d,scalar,%d>", RX, RYV)         \
+                       : launch_image<kThreads>(dev, fft2d_trunc_kernel<RX, RYV, false, kThreads>, smem, p, st, "fft2d_trunc_kernel<%d,%d,scalar,%d>", RX, RYV);
     switch (RY) { TFNO_IMG(2) TFNO_IMG(4) }
 #undef TFNO_IMG
     return TFNO_ERR_UNSUPPORTED;

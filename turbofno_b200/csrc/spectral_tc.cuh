@@ -1,49 +1,61 @@
 // Fused 1D spectral convolution for sm_100a with the channel contraction on the 5th-generation
-// tensor cores (tcgen05 + TMEM) and bulk-copy (TMA engine) input staging.
+// tensor cores (tcgen05 + TMEM) and bulk-copy (TMA engine) staging of input and output rows.
 // Same operator as spectral_tile_kernel<R,true,true,1>
 // (fusion_variants/1D_D_exp_fused_fft_cgemm_ifft/fused_fft_cgemm_ifft_7.cuh:9-222 in the
-// reference), restricted to N = 64 output channels, K <= 64, DY in {128, 256}.
+// reference), restricted to N = 64 output channels, K <= 96, DY in {128, 256}.
 //
-// One persistent CTA per SM, 512 threads in four warpgroups; setmaxnreg moves registers from
-// the two helper warpgroups to the two compute warpgroups (216 each), so that a compute thread
-// can hold a whole 64-point transform in registers:
+// One persistent CTA per SM, 768 threads in six warpgroups.  The transforms run on the 32-point
+// register FFT (fft32.cuh): a signal is spread over R = DY/32 lanes, a thread holds 32 samples, so
+// a compute thread needs ~110 registers and FOUR compute warps share a scheduler (the earlier
+// 64-point design had two at 216 registers and was bound by exposed latency: issue slots 37 % used).
+// setmaxnreg moves registers from the two helper warpgroups to the four compute warpgroups.
 //
-//   warps 0,2,4,6  forward  two half-teams {0,2} and {4,6}.  Input rows (DY*8 bytes each) arrive by
-//                           cp.async.bulk in a 2-stage shared-memory ring, CH = 64/R channels per
-//                           stage; a half-team takes one stage, each group of R lanes transforms
-//                           one channel (64-point register FFT + reduce-scatter), splits the 64
-//                           kept modes into tf32 hi/lo parts and stores them as the B operand
-//                           S[mode][kk] (K-major core matrices) in the half-team's own S buffer.
-//   warps 1,3,5,7  inverse  groups of R lanes read one output channel's 64 modes from the Re/Im
-//                           planes and run the zero-padded inverse transform; at DY = 256 the
-//                           rows are staged in shared memory and leave by cp.async.bulk, at
-//                           DY = 128 the lanes store directly.
-//   warps 8-11     hand-off tcgen05.ld of one accumulator row per thread -> Re/Im planes in shared
-//                           memory (a warp may only touch its own quarter of tensor memory, so
-//                           this needs four warps with distinct warp%4).
-//   warp 12        producer one thread arms a ring stage, CH lanes issue the bulk copies.
-//   warp 13        MMA      one thread issues tcgen05.mma kind::tf32, in chunk order:
-//                               D[128 x 64 modes] += Wt[128 x 8] * S[8 x 64]
-//                           Wt (the weights, rows 0-63 -> Re, 64-127 -> Im of output channel n,
-//                           columns kk = (chunk, Re|Im part, channel)) lives in tensor memory for
-//                           the whole kernel; fp32 accuracy comes from three tf32 products
-//                           (hi*hi + lo*hi + hi*lo).  Accumulators are double-buffered in TMEM.
+//   warps 0,2,..,14  forward  two half-teams {0,2,4,6} and {8,10,12,14}.  Input rows (DY*8 bytes
+//                             each) arrive by cp.async.bulk in a 2-stage shared-memory ring,
+//                             CH = 128/R channels per stage; a half-team takes one stage, each
+//                             group of R lanes transforms one channel (32-point register FFT +
+//                             exchange rounds), splits the 64 kept modes into tf32 hi/lo parts and
+//                             stores them as the B operand S[mode][kk] (K-major core matrices) in
+//                             the half-team's own S buffer.
+//   warps 1,3,..,15  inverse  groups of R lanes read one output channel's 64 modes from the Re/Im
+//                             planes and run the zero-padded inverse transform; at DY = 256 the
+//                             rows are staged in shared memory and leave by cp.async.bulk, at
+//                             DY = 128 the lanes store directly.
+//   warps 16-19      hand-off tcgen05.ld of one accumulator row per thread -> Re/Im planes in
+//                             shared memory (a warp may only touch its own quarter of tensor
+//                             memory, so this needs four warps with distinct warp%4).
+//   warp 20          producer one thread arms a ring stage, CH lanes issue the bulk copies.
+//   warp 21          MMA      one thread issues tcgen05.mma kind::tf32, in chunk order:
+//                                 D[128 x 64 modes] += Wt[128 x 8] * S[8 x 64]
+//                             Wt (the weights, rows 0-63 -> Re, 64-127 -> Im of output channel n,
+//                             columns kk = (chunk, channel, Re|Im part)) lives in tensor memory for
+//                             the whole kernel; fp32 accuracy comes from three tf32 products
+//                             (hi*hi + lo*hi + hi*lo).  Accumulators are double-buffered in TMEM.
 //
-// A scheduler partition hosts warps w, w+4, w+8, w+12: its two compute warps have the same role
-// and run in step, and both roles funnel through ONE copy of the unrolled 64-point transform (the
-// inverse is computed as swap(FFT(swap(u)))); together this keeps the instruction stream a
-// partition fetches short.
+// A scheduler partition hosts warps w, w+4, ...: its four compute warps have the same role, and
+// both roles funnel through ONE copy of the unrolled 32-point transform (the inverse is computed
+// as swap(FFT(swap(u)))); together this keeps the instruction stream a partition fetches short.
 //
 // Every wait is bounded: a wait that runs out sets `*status` and an abort flag, all roles leave
-// their loops, tensor memory is released, and the kernel returns.
+// their loops, outstanding copies and MMAs are drained, tensor memory is released, and the kernel
+// returns.
 #pragma once
 #include <cstdint>
-#include "fft64.cuh"
+#include "fft32.cuh"
 
 namespace tfno {
 namespace tc {
 
-constexpr int kTcThreads = 512;               // 4 warpgroups, see the role table above
+constexpr int kTcThreads = 768;             // 6 warpgroups, see the role table above
+constexpr int kComputeWarps = 16;           // 8 forward + 8 inverse
+constexpr int kHalfWarps = 4;               // forward warps per half-team
+constexpr int kInvWarps = 8;
+// setmaxnreg only moves registers inside the pool the CTA got at launch (threads x registers per
+// thread at launch: 768 x 80), and an increase that the pool cannot cover blocks for ever.
+constexpr int kLaunchRegs = 80;             // what ptxas reports for __launch_bounds__(768, 1)
+constexpr int kComputeRegs = 104;
+constexpr int kHelperRegs = 32;
+static_assert(512 * kComputeRegs + 256 * kHelperRegs <= kTcThreads * kLaunchRegs, "register pool of the CTA");
 constexpr int kStages = 2;                  // ring stages: one in flight per forward half-team
 constexpr int kLBO = 144;                   // bytes between K-adjacent core matrices of S (128 + 16 pad)
 constexpr uint32_t kSpinLimit = 1u << 22;   // polls (with back-off) before a wait gives up
@@ -59,7 +71,7 @@ constexpr unsigned kHelperIdleNs = TFNO_HELPER_IDLE_NS;   // sleep between polls
 #define TFNO_TRACE_STEP(slot, expr) [&]() { bool r_ = (expr); long long n_ = clock64(); tr_wait[slot] += n_ - tr_mark; tr_mark = n_; return r_; }()
 #define TFNO_TRACE_SINCE(slot) do { long long n_ = clock64(); tr_wait[slot] += n_ - tr_mark; tr_mark = n_; } while (0)
 #define TFNO_TRACE_WAIT(slot, expr) [&]() { long long t_ = clock64(); bool r_ = (expr); tr_wait[slot] += clock64() - t_; return r_; }()
-#define TFNO_TRACE_FLUSH() if (lane == 0 && p.trace) { long long* d_ = p.trace + ((long long)blockIdx.x * 16 + warp) * 12; d_[0] = clock64() - tr_t0; for (int i_ = 0; i_ < 11; ++i_) d_[1 + i_] = tr_wait[i_]; }
+#define TFNO_TRACE_FLUSH() if (lane == 0 && p.trace && warp < 16) { long long* d_ = p.trace + ((long long)blockIdx.x * 16 + warp) * 12; d_[0] = clock64() - tr_t0; for (int i_ = 0; i_ < 11; ++i_) d_[1 + i_] = tr_wait[i_]; }
 #else
 #define TFNO_TRACE_DECL
 #define TFNO_TRACE_MARK()
@@ -81,30 +93,37 @@ struct TcParams {
     long long* trace;           // optional per-warp cycle counters (builds with TFNO_TC_TRACE only)
 };
 
-// S holds ONE chunk (CH channels) per buffer; there are two buffers, one per forward half-team.
-// SBO: bytes between 8-mode groups of S.  The R lanes of a group store modes 64/R apart in the
-// same instruction, i.e. 8/R groups apart: SBO is the span of the chunk's K columns rounded up so that
-// (8/R)*SBO is 32 bytes (R = 4) or 64 bytes (R = 2) past a multiple of 128 -- both hold when SBO
-// is 16 past a multiple of 64 -- and the lanes of a warp fall into 32 different banks.
-__host__ __device__ inline int s_sbo(int R) {
-    const int span = (2 * (64 / R) / 4) * kLBO;           // one chunk: CH channels, Re and Im rows
+// SBO: bytes between 8-mode groups of the B operand S.  The contraction kernel of compact spectra
+// (cgemm_tc.cuh) stores 4-byte elements and uses s_sbo(4); the fused kernel stores the Re and Im
+// parts of a channel as one 8-byte element (column kk = 2*channel + part) and uses s_sbo_fused.
+__host__ __device__ inline int s_sbo(int R64) {
+    const int span = (2 * (64 / R64) / 4) * kLBO;           // one chunk: CH channels, Re and Im rows
     return ((span + 63) / 64) * 64 + 16;
 }
-__host__ __device__ inline int s_bytes(int R) { return 8 * s_sbo(R); }   // the hi or the lo array of one chunk buffer
+// R = DY/32 lanes per signal (adjacent lanes: lane = r + R*g), CH = 128/R channels per chunk.  A
+// half-warp's 8-byte stores (16/R channels, R lanes each 64/R modes apart) must cover all 32 banks:
+//   R = 8: two channels give {0,8} bytes, lanes r, r+1 are ONE mode group apart   -> SBO = 16 mod 128
+//   R = 4: four channels give 32 bytes, lanes r, r+1 are TWO mode groups apart    -> 2*SBO = 32 mod 128
+// both hold for a span that is a multiple of 64, plus 16.
+__host__ __device__ inline int s_sbo_fused(int R) {
+    const int span = (2 * (128 / R) / 4) * kLBO;
+    return ((span + 63) / 64) * 64 + 16;
+}
+__host__ __device__ inline int s_bytes(int R) { return 8 * s_sbo_fused(R); }   // the hi or the lo array of one chunk buffer
 
 template <int R> struct Geometry {
-    static constexpr int DY = 64 * R;
-    static constexpr int CH = 64 / R;                       // channels per chunk (= per ring stage)
+    static constexpr int DY = 32 * R;
+    static constexpr int GPW = 32 / R;                      // groups (channels) per warp
+    static constexpr int CH = kHalfWarps * GPW;             // channels per chunk (= per ring stage)
     static constexpr int ROW_BYTES = DY * 8;
-    static constexpr int ROW_STRIDE = ROW_BYTES + 16;       // pad: 8 rows x 16 B tile the 128-byte bank window
+    static constexpr int ROW_STRIDE = ROW_BYTES + 8 * R;    // pad: the 16/R rows a half-warp reads (8R bytes each) tile the 128-byte bank window
     static constexpr int STAGE_BYTES = CH * ROW_STRIDE;
     static constexpr int KSTEPS_PER_CHUNK = 2 * CH / 8;
     // Output rows are staged in shared memory and leave through the bulk-copy engine when there is
     // room (DY = 256); at DY = 128 the S buffers are twice as large and the lanes store directly.
-    // (direct 16-byte stores of sample pairs were also tried at DY = 256: 0.69 ms against 0.51 ms staged)
-    static constexpr bool STAGED_OUT = (R == 4);
-    static constexpr int OUT_ROWS = 32 / R;                 // output rows staged per inverse warp and task
-    static constexpr int OUT_STRIDE = ROW_BYTES + 16;       // padded like the input rows
+    static constexpr bool STAGED_OUT = (R == 8);
+    static constexpr int OUT_ROWS = GPW;                    // output rows staged per inverse warp and task
+    static constexpr int OUT_STRIDE = ROW_BYTES + 8 * R;    // padded like the input rows
     static constexpr int OUT_BYTES = STAGED_OUT ? OUT_ROWS * OUT_STRIDE : 0;   // per inverse warp
 };
 
@@ -115,10 +134,10 @@ __host__ inline size_t tc_smem_bytes(int K) {
     b += (size_t)kStages * G::STAGE_BYTES;        // ring
     (void)K;
     b += 2 * 2 * (size_t)s_bytes(R);              // two chunk buffers of S, hi and lo each
-    b += 4 * (size_t)G::OUT_BYTES;                // output staging, one per inverse warp
+    b += (size_t)kInvWarps * G::OUT_BYTES;        // output staging, one per inverse warp
     b += 2 * 64 * 256;                            // Re / Im planes [64 channels][64 modes] fp32
-    b += 2 * (size_t)R * 64 * 8;                  // twiddle tables
-    b += 256;                                     // barriers, tmem base, abort flag
+    b += 2 * (size_t)R * 32 * 8;                  // twiddle tables
+    b += 512;                                     // barriers, tmem base, abort flag
     return b + 1024;                              // slack for 1024-byte alignment of the base
 }
 
@@ -236,50 +255,63 @@ __device__ __forceinline__ float tf32_hi(float v) {
 // plane[part][channel n][mode m] fp32, 16-byte chunks XOR-swizzled with the channel
 __device__ __forceinline__ int plane_chunk(int n, int c) { return (c & ~7) | ((c & 7) ^ (n & 7)); }
 
+// Bounded wait that ignores the abort flag: used at teardown to let copies and MMAs that are
+// already in flight finish before shared and tensor memory are given back.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < (1u << 16); ++spin) {
+        if (mbar_try_wait(bar, parity)) return;
+        __nanosleep(64);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // INVERSE = true: second transform is the true inverse (done as swap(FFT(swap(u))), so that both
-// roles run the same forward 64-point code); false: a second forward transform.
+// roles run the same forward 32-point code); false: a second forward transform.
+// R = DY / 32 lanes per signal.
 template <int R, bool INVERSE>
 __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) {
     using G = Geometry<R>;
-    constexpr int CH = G::CH;
+    constexpr int CH = G::CH, GPW = G::GPW;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int K = p.K;
     const int NC = K / CH;                            // chunks per row
-    const int SBO = s_sbo(R), SBYTES = s_bytes(R);
+    const int SBO = s_sbo_fused(R), SBYTES = s_bytes(R);
     unsigned char* ring = base;
     unsigned char* sS = ring + kStages * G::STAGE_BYTES;            // [buffer 0: hi | lo][buffer 1: hi | lo]
     float* planes = reinterpret_cast<float*>(sS + 4 * SBYTES);      // [2][64][64]
-    unsigned char* ostage = reinterpret_cast<unsigned char*>(planes + 2 * 64 * 64);   // [4 warps][OUT_ROWS][OUT_STRIDE]
-    float2* twF = reinterpret_cast<float2*>(ostage + 4 * G::OUT_BYTES);
-    float2* twI = twF + R * 64;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(twI + R * 64);
+    unsigned char* ostage = reinterpret_cast<unsigned char*>(planes + 2 * 64 * 64);   // [8 warps][OUT_ROWS][OUT_STRIDE]
+    float2* twF = reinterpret_cast<float2*>(ostage + kInvWarps * G::OUT_BYTES);      // [R][32]
+    float2* twI = twF + R * 32;                                                       // [R][32]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(twI + R * 32);
     // barrier indices
-    constexpr int B_FULL = 0, B_EMPTY = kStages, B_SFULL = 2 * kStages, B_SEMPTY = B_SFULL + 8, B_AFULL = B_SEMPTY + 8,
-                  B_AEMPTY = B_AFULL + 2, B_PFULL = B_AEMPTY + 2, B_PEMPTY = B_PFULL + 1, B_STAGGER = B_PEMPTY + 1, B_COUNT = B_STAGGER + 2;
+    constexpr int B_FULL = 0, B_EMPTY = kStages, B_SFULL = 2 * kStages, B_SEMPTY = B_SFULL + 2, B_AFULL = B_SEMPTY + 2,
+                  B_AEMPTY = B_AFULL + 2, B_PFULL = B_AEMPTY + 2, B_PEMPTY = B_PFULL + 1, B_STAGGER = B_PEMPTY + 1,
+                  B_DRAIN = B_STAGGER + 2, B_COUNT = B_DRAIN + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // Roles.  A scheduler partition hosts warps w, w+4, w+8, w+12; giving it two compute warps of
-    // the SAME role keeps its instruction cache on one role's code.
-    const bool is_compute = warp < 8;
-    const bool is_fwd = is_compute && !(warp & 1);          // warps 0,2,4,6
-    const bool is_inv = is_compute && (warp & 1);           // warps 1,3,5,7
-    const bool is_xfer = warp >= 8 && warp < 12;            // TMEM quarter = warp & 3
+    // Roles.  A scheduler partition hosts warps w, w+4, ...; giving it compute warps of the SAME role
+    // keeps its instruction cache on one role's code.
+    const bool is_compute = warp < kComputeWarps;
+    const bool is_fwd = is_compute && !(warp & 1);          // warps 0,2,..,14
+    const bool is_inv = is_compute && (warp & 1);           // warps 1,3,..,15
+    const bool is_xfer = warp >= 16 && warp < 20;           // TMEM quarter = warp & 3
+    constexpr int kProducerWarp = 20, kMmaWarp = 21;
 
     // ---------------- set-up ----------------
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 2); }
-        for (int c = 0; c < 2; ++c) { mbar_init(bar(B_SFULL + c), 2); mbar_init(bar(B_SEMPTY + c), 1); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), kHalfWarps); }
+        for (int c = 0; c < 2; ++c) { mbar_init(bar(B_SFULL + c), kHalfWarps); mbar_init(bar(B_SEMPTY + c), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar(B_AFULL + b), 1); mbar_init(bar(B_AEMPTY + b), 4); }
         mbar_init(bar(B_PFULL), 4);
-        mbar_init(bar(B_PEMPTY), 4);
-        mbar_init(bar(B_STAGGER), 2);
-        mbar_init(bar(B_STAGGER + 1), 2);
+        mbar_init(bar(B_PEMPTY), kInvWarps);
+        mbar_init(bar(B_STAGGER), 4);
+        mbar_init(bar(B_STAGGER + 1), 4);
+        mbar_init(bar(B_DRAIN), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -287,8 +319,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    fill_forward_table<R>(twF, tid, kTcThreads);
-    fill_inverse_table<R>(twI, tid, kTcThreads, p.inv_gain, INVERSE);
+    fill_forward_table32<R>(twF, tid, kTcThreads);
+    fill_inverse_table32_folded<R>(twI, tid, kTcThreads, p.inv_gain, INVERSE);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -298,31 +330,35 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
     const long long first = blockIdx.x;
     const int n_it = first < p.rows ? (int)((p.rows - first + gridDim.x - 1) / gridDim.x) : 0;
     const long long n_loads = (long long)n_it * NC;
+    // Chunk c of a row belongs to forward half-team c & 1 and travels through ring stage c & 1, so a
+    // stage has ONE consuming half-team, which sees every phase of its barriers (a parity wait
+    // cannot tell "not yet" from "two phases on").  The k-th use of a stage is counted per stage.
+    // A row with a single chunk alternates the two stages between rows (one consumer again).
+    auto stage_of = [&](int it, int c) { return NC == 1 ? (it & 1) : (c & 1); };
+    auto use_of = [&](int it, int c) {
+        return NC == 1 ? (uint32_t)(it >> 1) : (uint32_t)it * (uint32_t)((NC - (c & 1) + 1) / 2) + (uint32_t)(c >> 1);
+    };
 
-    // weights into tensor memory: thread i of warps 8-11 owns row i: rows 0-63 produce Re, rows
-    // 64-127 produce Im of output channel n = i & 63
+    // weights into tensor memory: thread i of warps 16-19 owns row i: rows 0-63 produce Re, rows
+    // 64-127 produce Im of output channel n = i & 63.  Column kk of a chunk = 2 * channel + part:
+    // Re and Im of a channel are adjacent, matching the 8-byte stores of the forward warps.
     if (is_xfer) {
-        const int i = tid - 256, n = i & 63, im_row = i >> 6;
+        const int i = tid - 512, n = i & 63, im_row = i >> 6;
         const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        for (int c = 0; c < NC; ++c) {
-            for (int part = 0; part < 2; ++part) {
-                for (int k0 = 0; k0 < CH; k0 += 8) {
-                    uint32_t hi[8], lo[8];
+        for (int k0 = 0; k0 < K; k0 += 4) {
+            uint32_t hi[8], lo[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int k = c * CH + k0 + j;
-                        const float2 wv = __ldg(p.w + (long long)k * p.w_stride_k + (long long)n * p.w_stride_n);
-                        // Re row: [ Wr | -Wi ],  Im row: [ Wi | Wr ]  against  S = [ Xr ; Xi ]
-                        float v = im_row ? (part ? wv.x : wv.y) : (part ? -wv.y : wv.x);
-                        float h = tf32_hi(v);
-                        hi[j] = __float_as_uint(h);
-                        lo[j] = __float_as_uint(tf32_hi(v - h));
-                    }
-                    const uint32_t col = (uint32_t)(c * 2 * CH + part * CH + k0);
-                    TFNO_TMEM_ST8(trow + TM_WHI + col, hi);
-                    TFNO_TMEM_ST8(trow + TM_WLO + col, lo);
-                }
+            for (int j = 0; j < 8; ++j) {
+                const int k = k0 + (j >> 1), part = j & 1;
+                const float2 wv = __ldg(p.w + (long long)k * p.w_stride_k + (long long)n * p.w_stride_n);
+                // Re row: [ Wr | -Wi ],  Im row: [ Wi | Wr ]  against  S = [ Xr ; Xi ]
+                const float v = im_row ? (part ? wv.x : wv.y) : (part ? -wv.y : wv.x);
+                const float h = tf32_hi(v);
+                hi[j] = __float_as_uint(h);
+                lo[j] = __float_as_uint(tf32_hi(v - h));
             }
+            TFNO_TMEM_ST8(trow + TM_WHI + 2 * k0, hi);
+            TFNO_TMEM_ST8(trow + TM_WLO + 2 * k0, lo);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     }
@@ -332,11 +368,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
 
     TFNO_TRACE_DECL
     if (!is_compute) {
-        // ============ warpgroups 2 and 3: accumulator hand-off, data movement, MMA issue ============
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+        // ============ warpgroups 4 and 5: accumulator hand-off, data movement, MMA issue ============
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kHelperRegs) : "memory");
         if (is_xfer) {
             // accumulator row i = (part, channel) of this thread -> Re / Im planes in shared memory
-            const int i = tid - 256;
+            const int i = tid - 512;
             const int q = warp & 3;
             float* prow = planes + (i >> 6) * 4096 + (i & 63) * 64;
             bool ok = true;
@@ -361,10 +397,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(bar(B_AEMPTY + buf)); mbar_arrive(bar(B_PFULL)); }
             }
-        } else if (warp == 12) {
+        } else if (warp == kProducerWarp) {
             // producer: keeps the ring full
             auto issue_load = [&](long long L) {       // whole warp; lanes < CH copy one row each
-                const int s = (int)(L % kStages);
+                const int s = stage_of((int)(L / NC), (int)(L % NC));
                 const long long row = first + (L / NC) * gridDim.x;
                 const int c = (int)(L % NC);
                 if (lane == 0) mbar_arrive_expect_tx(bar(B_FULL + s), CH * G::ROW_BYTES);
@@ -375,14 +411,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 }
             };
             bool ok = true;
-            for (long long L = 0; L < n_loads && ok; ++L) {
-                const int s = (int)(L % kStages);
-                const uint32_t u = (uint32_t)(L / kStages);
+            long long L = 0;
+            for (; L < n_loads && ok; ++L) {
+                const int s = stage_of((int)(L / NC), (int)(L % NC));
+                const uint32_t u = use_of((int)(L / NC), (int)(L % NC));
                 ok = __all_sync(0xffffffffu, TFNO_TRACE_WAIT(0, mbar_wait(bar(B_EMPTY + s), (u & 1) ^ 1, abort_flag, p.status, 11, kHelperIdleNs)));
                 if (!ok) break;
                 issue_load(L);
             }
-        } else if (warp == 13 && lane == 0) {
+            if (*abort_flag) {
+                // copies already issued still write into this CTA's shared memory: let them land
+                for (long long j = (L >= kStages ? L - kStages : 0); j < L; ++j)
+                    mbar_drain(bar(B_FULL + stage_of((int)(j / NC), (int)(j % NC))), use_of((int)(j / NC), (int)(j % NC)) & 1);
+            }
+        } else if (warp == kMmaWarp && lane == 0) {
             // MMA issuer
             const uint32_t idesc = make_idesc_tf32(64);
             bool ok = true;
@@ -412,21 +454,24 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                     if (c == NC - 1) umma_commit(bar(B_AFULL + buf));
                 }
             }
+            // every MMA issued so far has finished before tensor memory is released
+            umma_commit(bar(B_DRAIN));
+            mbar_drain(bar(B_DRAIN), 0);
         }
     } else {
     // ======================= forward and inverse warps =======================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;" ::: "memory");
-    constexpr int GPW = 32 / R;                       // groups (channels) per warp
-    const int g = lane % GPW, r = lane / GPW;         // lane = g + GPW*r: the R lanes of a group are GPW apart
-    // forward: half-teams {0,2} and {4,6}: a scheduler partition (warps w and w+4) hosts one warp of
-    // each, and the second half-team starts half a task late, so that one warp's arithmetic
-    // overlaps the other's shuffles, shared-memory traffic and waits instead of colliding with it
-    const int half = (warp >> 2) & 1, wl = (warp >> 1) & 1;
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kComputeRegs) : "memory");
+    const int g = lane / R, r = lane % R;             // lane = r + R*g: the R lanes of a group are adjacent
+    // forward: half-teams {0,2,4,6} and {8,..,14}: a scheduler partition hosts two warps of each,
+    // and the second half-team starts half a task late, so that one half's arithmetic overlaps the
+    // other's shuffles, shared-memory traffic and waits instead of colliding with it
+    const int half = (warp >> 3) & 1, wl = (warp >> 1) & 3;
     bool stagger_pending = true;
     const int kl = wl * GPW + g;                      // forward: channel inside the chunk
-    const int qi = warp >> 1;                         // inverse: 0..3
-    constexpr int GROUPS = 128 / R;                   // inverse: channels per pass
+    const int qi = warp >> 1;                         // inverse: 0..7
+    constexpr int GROUPS = kInvWarps * GPW;           // inverse: channels per pass
     const int tasks_per_row = is_fwd ? (NC - half + 1) / 2 : 64 / GROUPS;
+    const float2 coef = is_fwd ? round1_coef32<R>(r) : inverse_fold_coef32<R>(r, INVERSE);   // forward: round 1; inverse: W_R^{-+r}
     bool alive = true;
 
     TFNO_TRACE_MARK();
@@ -434,20 +479,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
         const long long row = first + (long long)it * gridDim.x;
         for (int t = 0; t < tasks_per_row && alive; ++t) {
             TFNO_TRACE_SINCE(10);
-            float2 v[64];
+            float2 v[32];
             float sgn = 1.0f;
-            int c = 0, n = 0, s = 0;
+            int n = 0, s = 0;
             // ------------------------------ prologue ------------------------------
             if (is_fwd) {
-                c = half + 2 * t;
-                const long long L = (long long)it * NC + c;
-                s = (int)(L % kStages);
-                const uint32_t u = (uint32_t)(L / kStages);
+                const int c = half + 2 * t;
+                s = stage_of(it, c);
+                const uint32_t u = use_of(it, c);
                 alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(0, mbar_wait(bar(B_FULL + s), u & 1, abort_flag, p.status, 31)));
                 if (!alive) break;
                 const float2* srow = reinterpret_cast<const float2*>(ring + s * G::STAGE_BYTES + kl * G::ROW_STRIDE);
 #pragma unroll
-                for (int i = 0; i < 64; ++i) v[i] = srow[R * i + r];
+                for (int i = 0; i < 32; ++i) v[i] = srow[R * i + r];
                 // Hand the stage back for the next asynchronous (bulk-copy) overwrite.  The fence
                 // waits until this thread's loads have returned: __syncwarp alone does not, and a
                 // stage released with loads still in flight was overwritten under them.
@@ -455,7 +499,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_EMPTY + s));
                 TFNO_TRACE_SINCE(7);
-                sgn = (r & (R >> 1)) ? -1.0f : 1.0f;          // upper half of the group: spectrum rotated by 32
+                sgn = lane_rotated32<R>(r) ? -1.0f : 1.0f;
             } else {
                 if (t == 0) {
                     alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(0, mbar_wait(bar(B_PFULL), it & 1, abort_flag, p.status, 43)));
@@ -464,34 +508,44 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 n = t * GROUPS + qi * GPW + g;
                 const float* pre = planes + n * 64;
                 const float* pim = planes + 4096 + n * 64;
+                // u[m'] = T[m'] (C[m'] + c C[m'+32]), c = the lane's W_R^{-+r}; four m' per step
 #pragma unroll
-                for (int cc = 0; cc < 16; ++cc) {
-                    const float4 a = *reinterpret_cast<const float4*>(pre + plane_chunk(n, cc) * 4);
-                    const float4 b = *reinterpret_cast<const float4*>(pim + plane_chunk(n, cc) * 4);
+                for (int cc = 0; cc < 8; ++cc) {
+                    const float4 a0 = *reinterpret_cast<const float4*>(pre + plane_chunk(n, cc) * 4);
+                    const float4 b0 = *reinterpret_cast<const float4*>(pim + plane_chunk(n, cc) * 4);
+                    const float4 a1 = *reinterpret_cast<const float4*>(pre + plane_chunk(n, cc + 8) * 4);
+                    const float4 b1 = *reinterpret_cast<const float4*>(pim + plane_chunk(n, cc + 8) * 4);
                     const float4 t0 = *reinterpret_cast<const float4*>(twI + tw_index<R>(r, 4 * cc));
                     const float4 t1 = *reinterpret_cast<const float4*>(twI + tw_index<R>(r, 4 * cc + 2));
-                    const float2 u0 = cmul(make_float2(a.x, b.x), make_float2(t0.x, t0.y));
-                    const float2 u1 = cmul(make_float2(a.y, b.y), make_float2(t0.z, t0.w));
-                    const float2 u2 = cmul(make_float2(a.z, b.z), make_float2(t1.x, t1.y));
-                    const float2 u3 = cmul(make_float2(a.w, b.w), make_float2(t1.z, t1.w));
+                    const float2 u0 = cmul(cmadd(make_float2(a0.x, b0.x), coef, make_float2(a1.x, b1.x)), make_float2(t0.x, t0.y));
+                    const float2 u1 = cmul(cmadd(make_float2(a0.y, b0.y), coef, make_float2(a1.y, b1.y)), make_float2(t0.z, t0.w));
+                    const float2 u2 = cmul(cmadd(make_float2(a0.z, b0.z), coef, make_float2(a1.z, b1.z)), make_float2(t1.x, t1.y));
+                    const float2 u3 = cmul(cmadd(make_float2(a0.w, b0.w), coef, make_float2(a1.w, b1.w)), make_float2(t1.z, t1.w));
                     // inverse as swap(FFT(swap(u))): exchange re/im going in (and coming out below)
                     v[4 * cc] = INVERSE ? make_float2(u0.y, u0.x) : u0;
                     v[4 * cc + 1] = INVERSE ? make_float2(u1.y, u1.x) : u1;
                     v[4 * cc + 2] = INVERSE ? make_float2(u2.y, u2.x) : u2;
                     v[4 * cc + 3] = INVERSE ? make_float2(u3.y, u3.x) : u3;
                 }
+                if (t == tasks_per_row - 1) {
+                    // the planes have been read for the last time this row; the fence orders the
+                    // loads above before the release (their values are consumed only later)
+                    __threadfence_block();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(B_PEMPTY));
+                }
                 TFNO_TRACE_SINCE(8);
             }
 
-            // ------------------------------ the one 64-point transform ------------------------------
-            if (stagger_pending && (warp >> 2) == 1) {
-                // once: warps 4-7 wait until their partition mates have finished a first transform
+            // ------------------------------ the one 32-point transform ------------------------------
+            if (stagger_pending && (warp >> 3) == 1) {
+                // once: the second half waits until its partition mates have finished a first transform
                 alive = __all_sync(0xffffffffu, mbar_wait(bar(B_STAGGER + (is_fwd ? 0 : 1)), 0, abort_flag, p.status, 51));
                 if (!alive) break;
             }
-            fft64<-1>(v, sgn);
+            fft32<-1>(v, sgn);
             TFNO_TRACE_SINCE(6);
-            if (stagger_pending && (warp >> 2) == 0) {
+            if (stagger_pending && (warp >> 3) == 0) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_STAGGER + (is_fwd ? 0 : 1)));
             }
@@ -500,78 +554,70 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
             // ------------------------------ epilogue ------------------------------
             if (is_fwd) {
 #pragma unroll
-                for (int j = 0; j < 64; j += 2) {
+                for (int j = 0; j < 32; j += 2) {
                     const float4 tt = *reinterpret_cast<const float4*>(twF + tw_index<R>(r, j));
-                    v[slot(j)] = cmul(v[slot(j)], make_float2(tt.x, tt.y));
-                    v[slot(j + 1)] = cmul(v[slot(j + 1)], make_float2(tt.z, tt.w));
+                    v[slot32(j)] = cmul(v[slot32(j)], make_float2(tt.x, tt.y));
+                    v[slot32(j + 1)] = cmul(v[slot32(j + 1)], make_float2(tt.z, tt.w));
                 }
-                // reduce-scatter over the R lanes of the group (GPW apart)
-                exchange_round_top(v, (R >> 1) * GPW);
-                if constexpr (R >= 4) exchange_round<16>(v, (R >> 2) * GPW, (r & (R >> 2)) != 0);
-                // lane r now holds modes 64/R*r + j, j < 64/R, in v[slot(j)]
+                // exchange rounds over the R adjacent lanes of the group
+                exchange_round1_32(v, R >> 1, coef);
+                exchange_round2_32(v, R >> 2);
+                if constexpr (R >= 8) exchange_round_32<8>(v, R >> 3, (r & (R >> 3)) != 0);
+                // lane r now holds modes 64/R*r + j, j < 64/R, in v[slot32(j)]
                 TFNO_TRACE_SINCE(8);
                 // this half-team's S buffer is free once the MMAs of its previous chunk have completed
                 const uint32_t jchunk = (uint32_t)it * (uint32_t)tasks_per_row + (uint32_t)t;
                 alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(1, mbar_wait(bar(B_SEMPTY + half), (jchunk & 1) ^ 1, abort_flag, p.status, 32)));
                 if (!alive) break;
                 constexpr int PER = 64 / R;
-                const int kk_re = kl, kk_im = CH + kl;                 // K row inside the chunk buffer
                 unsigned char* sbuf = sS + 2 * half * SBYTES;
-                unsigned char* hi_re = sbuf + (kk_re >> 2) * kLBO + (kk_re & 3) * 4;
-                unsigned char* hi_im = sbuf + (kk_im >> 2) * kLBO + (kk_im & 3) * 4;
+                unsigned char* hi_base = sbuf + (kl >> 1) * kLBO + (kl & 1) * 8;     // kk = 2*kl (Re), 2*kl + 1 (Im)
 #pragma unroll
                 for (int j = 0; j < PER; ++j) {
                     const int m = PER * r + j;
                     const int off = (m >> 3) * SBO + (m & 7) * 16;
-                    const float xr = v[slot(j)].x, xi = v[slot(j)].y;
+                    const float xr = v[slot32(j)].x, xi = v[slot32(j)].y;
                     const float hr = tf32_hi(xr), hi = tf32_hi(xi);
-                    *reinterpret_cast<float*>(hi_re + off) = hr;
-                    *reinterpret_cast<float*>(hi_re + SBYTES + off) = xr - hr;
-                    *reinterpret_cast<float*>(hi_im + off) = hi;
-                    *reinterpret_cast<float*>(hi_im + SBYTES + off) = xi - hi;
+                    *reinterpret_cast<float2*>(hi_base + off) = make_float2(hr, hi);
+                    *reinterpret_cast<float2*>(hi_base + SBYTES + off) = make_float2(xr - hr, xi - hi);
                 }
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_SFULL + half));
                 TFNO_TRACE_SINCE(9);
             } else {
-                if (t == tasks_per_row - 1) {
-                    // the planes have been read for the last time this row (values are in use above)
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(B_PEMPTY));
-                }
-                // Stage the warp's OUT_ROWS output rows in shared memory and hand each row to the
-                // bulk-copy engine: the rows leave as full lines instead of 32-byte pieces through
-                // the load/store unit.  The lanes that issue the copies first wait until their
-                // previous copies have finished reading the staging buffer.
                 if constexpr (!G::STAGED_OUT) {
-                    // Lanes r and r ^ 1 of a group (GPW lanes apart) own samples that alternate in
+                    // Lanes r and r ^ 1 of a group (adjacent) own samples that alternate in
                     // memory: each stores 16 bytes (its own sample and the neighbour's) for every
                     // second j2 and they swap the foreign halves with a shuffle -- half as many
                     // store instructions, each filling whole 32-byte sectors.
                     const bool odd = (r & 1) != 0;
                     float2* dst = p.y + row * p.y_stride_row + (long long)n * p.y_stride_n + (odd ? R : 0) + (r & ~1);
 #pragma unroll
-                    for (int n2 = 0; n2 < 32; ++n2) {
-                        const float2 a = v[slot(2 * n2)], b = v[slot(2 * n2 + 1)];
+                    for (int n2 = 0; n2 < 16; ++n2) {
+                        const float2 a = v[slot32(2 * n2)], b = v[slot32(2 * n2 + 1)];
                         const float2 ev = INVERSE ? make_float2(a.y, a.x) : a;       // this lane's sample R*(2*n2) + r
                         const float2 od = INVERSE ? make_float2(b.y, b.x) : b;       // this lane's sample R*(2*n2+1) + r
                         const float2 send = odd ? ev : od;
                         float2 got;
-                        got.x = __shfl_xor_sync(0xffffffffu, send.x, GPW);
-                        got.y = __shfl_xor_sync(0xffffffffu, send.y, GPW);
+                        got.x = __shfl_xor_sync(0xffffffffu, send.x, 1);
+                        got.y = __shfl_xor_sync(0xffffffffu, send.y, 1);
                         *reinterpret_cast<float4*>(dst + 2 * R * n2) =
                             odd ? make_float4(got.x, got.y, od.x, od.y) : make_float4(ev.x, ev.y, got.x, got.y);
                     }
                 } else {
+                // Stage the warp's OUT_ROWS output rows in shared memory and hand each row to the
+                // bulk-copy engine: the rows leave as full lines instead of 32-byte pieces through
+                // the load/store unit.  The lanes that issue the copies first wait until their
+                // previous copies have finished reading the staging buffer.
                 unsigned char* ost = ostage + qi * G::OUT_BYTES;
                 if (lane < G::OUT_ROWS) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 __syncwarp();
                 TFNO_TRACE_SINCE(2);
                 float2* srow_out = reinterpret_cast<float2*>(ost + g * G::OUT_STRIDE);
 #pragma unroll
-                for (int j2 = 0; j2 < 64; ++j2) {
-                    const float2 o = v[slot(j2)];
+                for (int j2 = 0; j2 < 32; ++j2) {
+                    const float2 o = v[slot32(j2)];
                     srow_out[R * j2 + r] = INVERSE ? make_float2(o.y, o.x) : o;
                 }
                 TFNO_TRACE_SINCE(3);
