@@ -138,9 +138,9 @@ int tfno_exec_host(tfno_plan* plan, const void* x_host, const void* w_host, void
  * cudaMemcpy (fusion_variants/1D_D_exp_fused_fft_cgemm_ifft/fused.cu:116). */
 int tfno_plan_set_host_chunk(tfno_plan* plan, long long batch_items);
 
-/* Writes the comma-separated names of the kernels (and library calls) one tfno_exec of this plan
- * launches, in launch order, e.g. "spectral_tc_kernel<4,1>" or
- * "fft2d_trunc_kernel<4,4,paired,256>,cgemm_tc_kernel<128>,ifft2d_pad_kernel<4,4,paired,256>".
+/* Writes the names of the kernels (and library calls) one tfno_exec of this plan launches, in
+ * launch order and separated by ';', e.g. "spectral_tc_kernel<8,1>" or
+ * "fft2d_trunc_kernel<4,4,paired,256>;cgemm_tc_kernel<128>;ifft2d_pad_kernel<4,4,paired,256>".
  * It is produced by a dry run of the dispatch code tfno_exec itself executes.  Stands in for reading
  * which table entry a reference driver launches
  * (fusion_variants/1D_D_exp_fused_fft_cgemm_ifft/fused.cu:15-16,126). */

@@ -4,14 +4,16 @@
 //   fusion_variants/1D_E_baseline/fused.cu:13-63   and   fusion_variants/2D_E_baseline/fused_trunc_2D.cu:13-71
 // and the hand-written cgemm kernel of fusion_variants/1D_E_baseline/cgemm.cuh, launched with the
 // grid / block / shared-memory sizes the reference drivers use, around cuFFT calls in the
-// reference's order.  Arithmetic follows FNO semantics (alpha = 1, beta = 0, CUFFT_INVERSE,
-// 1/len scale) so that the result is comparable with the oracle; the reference's main() is
-// compiled too (renamed) but never called.
+// reference's order.  Arithmetic follows FNO semantics by default (alpha = 1, beta = 0,
+// CUFFT_INVERSE, 1/len scale) so that the result is comparable with the oracle; the reference's
+// main() is compiled too (renamed) but never called.
 //
-// Usage:  ref_harness_{1d,2d} <x.bin> <w.bin> <y.bin> <bs> <dimX|DX> <DY> <N> <K> [cublas]
+// Usage:  ref_harness_{1d,2d} <x.bin> <w.bin> <y.bin> <bs> <dimX|DX> <DY> <N> <K> [cublas] [as-shipped]
 //   x.bin: complex64, reference layout [K][bs*dimX][DY] or [K][bs][DX][DY];  w.bin: [N][K];
 //   y.bin (written): [N][...] like x.  With "cublas" the GEMM is cublasCgemm as in variant E,
-//   otherwise the reference's cgemm kernel.
+//   otherwise the reference's cgemm kernel.  With "as-shipped" the arithmetic is the one the
+//   reference drivers run (fusion_variants/1D_E_baseline/fused.cu:116,186-190): alpha = (1,-1),
+//   beta = (-1,1) applied once to a zeroed C, second transform CUFFT_FORWARD, no scaling.
 #define main tfno_reference_main_unused
 #if HARNESS_RANK == 1
 #include "fusion_variants/1D_E_baseline/fused.cu"
@@ -37,10 +39,14 @@ static bool read_file(const char* path, void* dst, size_t bytes) {
 #define REQUIRE(cond, msg) do { if (!(cond)) { fprintf(stderr, "ref_harness: %s\n", msg); return 1; } } while (0)
 
 int main(int argc, char** argv) {
-    REQUIRE(argc >= 9, "usage: <x.bin> <w.bin> <y.bin> <bs> <dimX|DX> <DY> <N> <K> [cublas]");
+    REQUIRE(argc >= 9, "usage: <x.bin> <w.bin> <y.bin> <bs> <dimX|DX> <DY> <N> <K> [cublas] [as-shipped]");
     const long long bs = atoll(argv[4]);
     const int d1 = atoi(argv[5]), DY = atoi(argv[6]), N = atoi(argv[7]), K = atoi(argv[8]);
-    const bool use_cublas = argc > 9 && !strcmp(argv[9], "cublas");
+    bool use_cublas = false, as_shipped = false;
+    for (int a = 9; a < argc; ++a) {
+        if (!strcmp(argv[a], "cublas")) use_cublas = true;
+        else if (!strcmp(argv[a], "as-shipped")) as_shipped = true;
+    }
 #if HARNESS_RANK == 1
     const long long rows = bs * d1, unit = DY;          // signals per channel, elements per signal
     const long long M = rows * 64;
@@ -89,6 +95,7 @@ int main(int argc, char** argv) {
     REQUIRE(cudaDeviceSynchronize() == cudaSuccess, "truncation kernel");
 
     float2 alpha = {1.f, 0.f}, beta = {0.f, 0.f};
+    if (as_shipped) { alpha = {1.f, -1.f}; beta = {-1.f, 1.f}; }
     if (use_cublas) {
         cublasHandle_t handle;
         REQUIRE(cublasCreate(&handle) == CUBLAS_STATUS_SUCCESS, "cublasCreate");
@@ -113,9 +120,9 @@ int main(int argc, char** argv) {
     direct_copy_colmajor_float4_zero_padding_2d<<<gridDim_copy2, blockDim_copy>>>(dC, dY2, DY, DX, (int)(bs * N), 64, 64);
 #endif
     REQUIRE(cudaDeviceSynchronize() == cudaSuccess, "zero-padding kernel");
-    REQUIRE(cufftExecC2C(iplan, (cufftComplex*)dY2, (cufftComplex*)dY2, CUFFT_INVERSE) == CUFFT_SUCCESS, "cufft inverse");
+    REQUIRE(cufftExecC2C(iplan, (cufftComplex*)dY2, (cufftComplex*)dY2, as_shipped ? CUFFT_FORWARD : CUFFT_INVERSE) == CUFFT_SUCCESS, "second cufft");
     REQUIRE(cudaMemcpy(hy.data(), dY2, yout * 8, cudaMemcpyDeviceToHost) == cudaSuccess, "copy back");
-    const float s = 1.0f / (float)unit;
+    const float s = as_shipped ? 1.0f : 1.0f / (float)unit;
     for (auto& v : hy) { v.x *= s; v.y *= s; }
     FILE* f = fopen(argv[3], "wb");
     REQUIRE(f, "cannot write y");

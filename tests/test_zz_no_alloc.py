@@ -36,7 +36,9 @@ def test_static_scratch_layer_matches_plan_path_twice_in_a_row(cuda):
     other = t.spectral_conv2d_static(torch.from_numpy(to_reference_layout(x2)).to(cuda), wd)
     second = t.spectral_conv2d_static(xd, wd)
     torch.cuda.synchronize()
-    # same kernels, same arithmetic order: the tolerance of the parity tests (in fact bit-identical)
+    # Same image kernels; the contraction runs on the FP32 kernel here and on the tensor cores in
+    # the plan (K = 32, N = 64), so the two agree to rounding: the tolerance of the parity tests.
+    assert "cgemm_tc_kernel" in ",".join(plan.kernels())
     assert_close(first.cpu().numpy(), expected.cpu().numpy(), "static entry point, first call")
     assert_close(second.cpu().numpy(), expected.cpu().numpy(), "static entry point, second call")
     assert torch.equal(first.view(torch.float32), second.view(torch.float32))
@@ -64,4 +66,9 @@ def test_static_scratch_limit_and_bad_arguments(cuda):
     assert lib.tfno_spectral_conv2d_static(1, 256, 256, 12, 64, p, p, p, 1.0, 0.0, None) == _lib.ERR_UNSUPPORTED
     assert lib.tfno_spectral_conv2d_static(1, 256, 256, 8, 64, None, p, p, 1.0, 0.0, None) == _lib.ERR_INVALID_ARG
     assert lib.tfno_spectral_conv2d_static(1, 256, 256, 8, 64, vp(buf.data_ptr() + 8), p, p, 1.0, 0.0, None) == _lib.ERR_INVALID_ARG
+    # sizes whose byte count does not fit 64 bits must be refused too, not wrap around and pass
+    assert lib.tfno_spectral_conv2d_static(1 << 58, 256, 256, 64, 64, p, p, p, 1.0, 0.0, None) == _lib.ERR_SCRATCH_LIMIT
+    assert lib.tfno_spectral_conv2d_static((1 << 49) + 1, 256, 256, 8, 64, p, p, p, 1.0, 0.0, None) == _lib.ERR_SCRATCH_LIMIT
+    # a K that the contraction's shared memory cannot hold is refused before the first launch
+    assert lib.tfno_spectral_conv2d_static(1, 128, 128, 512, 64, p, p, p, 1.0, 0.0, None) in (_lib.ERR_UNSUPPORTED, _lib.ERR_SCRATCH_LIMIT)
     assert float(torch.ones(4, device=cuda).sum()) == 4.0

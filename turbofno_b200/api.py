@@ -20,14 +20,38 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr())
 
 
-def _stream_ptr(stream=None):
-    s = stream if stream is not None else torch.cuda.current_stream()
+def _stream_ptr(stream=None, device=None):
+    """cudaStream_t of `stream`, or of the current stream of `device` (not of the current device:
+    the tensors decide where the work runs)."""
+    s = stream if stream is not None else torch.cuda.current_stream(device)
     return ctypes.c_void_p(s.cuda_stream)
 
 
 def _check_tensor(t, name):
     if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.complex64 and t.is_contiguous()):
         raise TypeError("%s must be a contiguous complex64 CUDA tensor" % name)
+
+
+def expected_shapes(rank, layout, B, K, N, DY, DX=None):
+    """Shapes (x, w, y) a plan accepts, from its problem alone.  Reference layout: x[K, B, ...],
+    w[N, K], y[N, B, ...]; batch-major: x[B, K, ...], w[K, N], y[B, N, ...]."""
+    tail = (DY,) if rank == 1 else (DX, DY)
+    if layout == "reference":
+        return (K, B) + tail, (N, K), (N, B) + tail
+    return (B, K) + tail, (K, N), (B, N) + tail
+
+
+def check_shapes(rank, layout, B, K, N, DY, DX, x_shape, w_shape, y_shape=None):
+    """Raises ValueError unless the tensors have exactly the shapes the plan was made for.  The
+    kernels trust the plan's sizes (bulk copies included): a smaller tensor would be read or
+    written out of bounds on the device, so the mirror refuses it on the host."""
+    ex, ew, ey = expected_shapes(rank, layout, B, K, N, DY, DX)
+    if tuple(x_shape) != ex:
+        raise ValueError("x has shape %s, the plan needs %s" % (tuple(x_shape), ex))
+    if tuple(w_shape) != ew:
+        raise ValueError("w has shape %s, the plan needs %s" % (tuple(w_shape), ew))
+    if y_shape is not None and tuple(y_shape) != ey:
+        raise ValueError("y has shape %s, the plan needs %s" % (tuple(y_shape), ey))
 
 
 class Handle:
@@ -120,18 +144,46 @@ class SpectralConv:
         return ((p.N, self.B) if self.layout == "reference" else (self.B, p.N)) + tail
 
     def workspace(self, device):
+        """The plan's own scratch buffer (allocated on first use).  It serves ONE stream at a time:
+        callers that run the same plan on several streams concurrently pass their own `workspace`."""
         if self.workspace_bytes and (self._ws is None or self._ws.device != device):
             self._ws = torch.empty(self.workspace_bytes, dtype=torch.uint8, device=device)
         return self._ws
 
+    def kernels(self):
+        """Names of the kernels one call launches, in order (tfno_plan_kernels)."""
+        buf = ctypes.create_string_buffer(1024)
+        check(self.lib.tfno_plan_kernels(self._plan, buf, len(buf)), "tfno_plan_kernels")
+        return buf.value.decode().split(";")
+
+    def set_host_chunk(self, batch_items):
+        """Batch items per pipeline chunk of exec_host; call before the first exec_host."""
+        check(self.lib.tfno_plan_set_host_chunk(self._plan, int(batch_items)), "tfno_plan_set_host_chunk")
+
+    def _check_call(self, x, w, y, workspace):
+        p = self.problem
+        check_shapes(self.rank, self.layout, self.B, p.K, p.N, p.DY, p.DX, x.shape, w.shape, None if y is None else y.shape)
+        dev = torch.device("cuda", self.handle.device)
+        for name, t in (("x", x), ("w", w), ("y", y), ("workspace", workspace)):
+            if t is not None and t.device != dev:
+                raise ValueError("%s is on %s, the plan's handle on %s" % (name, t.device, dev))
+        if workspace is not None:
+            if not (workspace.is_cuda and workspace.is_contiguous()):
+                raise ValueError("workspace must be a contiguous CUDA tensor")
+            if workspace.numel() * workspace.element_size() < self.workspace_bytes:
+                raise ValueError("workspace holds %d bytes, the plan needs %d" %
+                                 (workspace.numel() * workspace.element_size(), self.workspace_bytes))
+
     def __call__(self, x, w, y=None, workspace=None, stream=None):
         _check_tensor(x, "x")
         _check_tensor(w, "w")
+        if y is not None:
+            _check_tensor(y, "y")
+        self._check_call(x, w, y, workspace)
         if y is None:
             y = torch.empty(self.out_shape(), dtype=torch.complex64, device=x.device)
-        _check_tensor(y, "y")
         ws = workspace if workspace is not None else self.workspace(x.device)
-        check(self.lib.tfno_exec(self._plan, _ptr(x), _ptr(w), _ptr(y), _ptr(ws), _stream_ptr(stream)), "tfno_exec")
+        check(self.lib.tfno_exec(self._plan, _ptr(x), _ptr(w), _ptr(y), _ptr(ws), _stream_ptr(stream, x.device)), "tfno_exec")
         return y
 
     def exec_host(self, x_host, w_host, y_host):
@@ -139,6 +191,8 @@ class SpectralConv:
         for t in (x_host, w_host, y_host):
             if t.is_cuda or t.dtype != torch.complex64 or not t.is_contiguous():
                 raise TypeError("exec_host needs contiguous complex64 host tensors")
+        p = self.problem
+        check_shapes(self.rank, self.layout, self.B, p.K, p.N, p.DY, p.DX, x_host.shape, w_host.shape, y_host.shape)
         check(self.lib.tfno_exec_host(self._plan, ctypes.c_void_p(x_host.data_ptr()), ctypes.c_void_p(w_host.data_ptr()),
                                       ctypes.c_void_p(y_host.data_ptr())), "tfno_exec_host")
         return y_host
@@ -169,7 +223,7 @@ def fused_fft_cgemm_ifft(M, N, K, FFT_input, B, C, FFT_output, alpha=1 + 0j, bet
     h = Handle.get(FFT_input.device.index)
     a, b = complex(alpha), complex(beta)
     check(h.lib.tfno_fused_fft_cgemm_ifft(h._h, _log2(DY), M, N, K, _ptr(FFT_input), _ptr(B), _ptr(C), _ptr(FFT_output),
-                                          a.real, a.imag, b.real, b.imag, _stream_ptr(stream)), "tfno_fused_fft_cgemm_ifft")
+                                          a.real, a.imag, b.real, b.imag, _stream_ptr(stream, FFT_input.device)), "tfno_fused_fft_cgemm_ifft")
     return FFT_output
 
 
@@ -177,7 +231,7 @@ def fused_fft_cgemm(M, N, K, FFT_input, B, C, alpha=1 + 0j, beta=0j, DY=128, str
     h = Handle.get(FFT_input.device.index)
     a, b = complex(alpha), complex(beta)
     check(h.lib.tfno_fused_fft_cgemm(h._h, _log2(DY), M, N, K, _ptr(FFT_input), _ptr(B), _ptr(C),
-                                     a.real, a.imag, b.real, b.imag, _stream_ptr(stream)), "tfno_fused_fft_cgemm")
+                                     a.real, a.imag, b.real, b.imag, _stream_ptr(stream, FFT_input.device)), "tfno_fused_fft_cgemm")
     return C
 
 
@@ -185,7 +239,7 @@ def fused_cgemm_ifft(M, N, K, A, B, C, FFT_output, alpha=1 + 0j, beta=0j, DY=128
     h = Handle.get(A.device.index)
     a, b = complex(alpha), complex(beta)
     check(h.lib.tfno_fused_cgemm_ifft(h._h, _log2(DY), M, N, K, _ptr(A), _ptr(B), _ptr(C), _ptr(FFT_output),
-                                      a.real, a.imag, b.real, b.imag, _stream_ptr(stream)), "tfno_fused_cgemm_ifft")
+                                      a.real, a.imag, b.real, b.imag, _stream_ptr(stream, A.device)), "tfno_fused_cgemm_ifft")
     return FFT_output
 
 
@@ -193,31 +247,31 @@ def cgemm(M, N, K, A, B, C, alpha=1 + 0j, beta=0j, stream=None):
     h = Handle.get(A.device.index)
     a, b = complex(alpha), complex(beta)
     check(h.lib.tfno_cgemm(h._h, M, N, K, _ptr(A), _ptr(B), _ptr(C), a.real, a.imag, b.real, b.imag,
-                           _stream_ptr(stream)), "tfno_cgemm")
+                           _stream_ptr(stream, A.device)), "tfno_cgemm")
     return C
 
 
 def fft_stride_DY(inp, out, total_signals, DY, stream=None):
     h = Handle.get(inp.device.index)
-    check(h.lib.tfno_fft_stride_DY(h._h, _log2(DY), _ptr(inp), _ptr(out), total_signals, _stream_ptr(stream)), "tfno_fft_stride_DY")
+    check(h.lib.tfno_fft_stride_DY(h._h, _log2(DY), _ptr(inp), _ptr(out), total_signals, _stream_ptr(stream, inp.device)), "tfno_fft_stride_DY")
     return out
 
 
 def ifft_stride_DY(inp, out, total_signals, DY, stream=None):
     h = Handle.get(inp.device.index)
-    check(h.lib.tfno_ifft_stride_DY(h._h, _log2(DY), _ptr(inp), _ptr(out), total_signals, _stream_ptr(stream)), "tfno_ifft_stride_DY")
+    check(h.lib.tfno_ifft_stride_DY(h._h, _log2(DY), _ptr(inp), _ptr(out), total_signals, _stream_ptr(stream, inp.device)), "tfno_ifft_stride_DY")
     return out
 
 
 def fft_stride(inp, out, DY, total_columns, DX, stream=None):
     h = Handle.get(inp.device.index)
-    check(h.lib.tfno_fft_stride(h._h, _log2(DX), _ptr(inp), _ptr(out), DY, total_columns, _stream_ptr(stream)), "tfno_fft_stride")
+    check(h.lib.tfno_fft_stride(h._h, _log2(DX), _ptr(inp), _ptr(out), DY, total_columns, _stream_ptr(stream, inp.device)), "tfno_fft_stride")
     return out
 
 
 def ifft_stride(inp, out, DY, total_columns, DX, stream=None):
     h = Handle.get(inp.device.index)
-    check(h.lib.tfno_ifft_stride(h._h, _log2(DX), _ptr(inp), _ptr(out), DY, total_columns, _stream_ptr(stream)), "tfno_ifft_stride")
+    check(h.lib.tfno_ifft_stride(h._h, _log2(DX), _ptr(inp), _ptr(out), DY, total_columns, _stream_ptr(stream, inp.device)), "tfno_ifft_stride")
     return out
 
 
@@ -229,14 +283,21 @@ def spectral_conv2d_static(x, w, y=None, alpha=1 + 0j, stream=None):
     reference layout; y is allocated here by torch only if the caller does not pass one."""
     _check_tensor(x, "x")
     _check_tensor(w, "w")
+    if x.dim() != 4 or w.dim() != 2:
+        raise ValueError("x must be [K, bs, DX, DY] and w [N, K]")
     K, bs, DX, DY = x.shape
     N = w.shape[0]
+    if y is not None:
+        _check_tensor(y, "y")
+    check_shapes(2, "reference", bs, K, N, DY, DX, x.shape, w.shape, None if y is None else y.shape)
+    for name, t in (("w", w), ("y", y)):
+        if t is not None and t.device != x.device:
+            raise ValueError("%s is on %s, x on %s" % (name, t.device, x.device))
     if y is None:
         y = torch.empty((N, bs, DX, DY), dtype=torch.complex64, device=x.device)
-    _check_tensor(y, "y")
     lib = _lib.load()
     a = complex(alpha)
     with torch.cuda.device(x.device):
         check(lib.tfno_spectral_conv2d_static(bs, DX, DY, K, N, _ptr(x), _ptr(w), _ptr(y), a.real, a.imag,
-                                              _stream_ptr(stream)), "tfno_spectral_conv2d_static")
+                                              _stream_ptr(stream, x.device)), "tfno_spectral_conv2d_static")
     return y

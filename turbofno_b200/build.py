@@ -89,6 +89,16 @@ def build_drivers(force=False):
             ])
             _stamp(exe, deps, extra=cfg)
         outs.append(exe)
+    # the example port of a reference-style driver (kernel tables of include/TurboFNO.h)
+    port_src = os.path.join(PKG, "drivers", "compat_port.cu")
+    port_exe = os.path.join(BIN, "compat_port")
+    if force or _newer(port_exe, [port_src] + hdrs):
+        subprocess.check_call([
+            "nvcc", "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-I" + os.path.join(ROOT, "include"),
+            port_src, "-o", port_exe, "-L" + PKG, "-lturbofno_b200", "-Xlinker", "-rpath=" + PKG,
+        ])
+        _stamp(port_exe, [port_src] + hdrs)
+    outs.append(port_exe)
     return outs
 
 

@@ -21,8 +21,8 @@ struct DeviceInfo {
     int max_smem_optin = 0;
     bool use_tensor_cores = true;   // tcgen05 fused kernel where its shape limits allow
     int* status = nullptr;          // device word written by kernels whose bounded waits ran out
-    // Dry run: when set, every launcher appends the name of the kernel it would launch (comma
-    // separated) and launches nothing.  tfno_plan_kernels reports a plan's kernels this way, from
+    // Dry run: when set, every launcher appends the name of the kernel it would launch (separated
+    // by ';') and launches nothing.  tfno_plan_kernels reports a plan's kernels this way, from
     // the same dispatch code tfno_exec runs.
     char* record = nullptr;
     size_t record_cap = 0;
@@ -41,7 +41,7 @@ inline bool record_launch(const DeviceInfo& dev, const char* fmt, int a = 0, int
     const size_t used = std::strlen(dev.record);
     if (used + 2 < dev.record_cap) {
         int n = 0;
-        if (used) n = std::snprintf(dev.record + used, dev.record_cap - used, ",");
+        if (used) n = std::snprintf(dev.record + used, dev.record_cap - used, ";");
         std::snprintf(dev.record + used + n, dev.record_cap - used - n, fmt, a, b, c, d);
     }
     return true;

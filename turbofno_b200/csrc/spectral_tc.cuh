@@ -71,7 +71,7 @@ constexpr unsigned kHelperIdleNs = TFNO_HELPER_IDLE_NS;   // sleep between polls
 #define TFNO_TRACE_STEP(slot, expr) [&]() { bool r_ = (expr); long long n_ = clock64(); tr_wait[slot] += n_ - tr_mark; tr_mark = n_; return r_; }()
 #define TFNO_TRACE_SINCE(slot) do { long long n_ = clock64(); tr_wait[slot] += n_ - tr_mark; tr_mark = n_; } while (0)
 #define TFNO_TRACE_WAIT(slot, expr) [&]() { long long t_ = clock64(); bool r_ = (expr); tr_wait[slot] += clock64() - t_; return r_; }()
-#define TFNO_TRACE_FLUSH() if (lane == 0 && p.trace && warp < 16) { long long* d_ = p.trace + ((long long)blockIdx.x * 16 + warp) * 12; d_[0] = clock64() - tr_t0; for (int i_ = 0; i_ < 11; ++i_) d_[1 + i_] = tr_wait[i_]; }
+#define TFNO_TRACE_FLUSH() if (lane == 0 && p.trace && warp < 24) { long long* d_ = p.trace + ((long long)blockIdx.x * 24 + warp) * 12; d_[0] = clock64() - tr_t0; for (int i_ = 0; i_ < 11; ++i_) d_[1 + i_] = tr_wait[i_]; }
 #else
 #define TFNO_TRACE_DECL
 #define TFNO_TRACE_MARK()

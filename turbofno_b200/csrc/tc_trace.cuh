@@ -5,7 +5,7 @@
 #pragma once
 #ifdef TFNO_TC_TRACE
 
-constexpr int kTraceWarps = 16, kTraceSlots = 12;
+constexpr int kTraceWarps = 24, kTraceSlots = 12;
 
 // counter buffer of the device, sized from its SM count; cleared when `clear` is set
 inline long long* tc_trace_buffer(const DeviceInfo& dev, bool clear) {
@@ -24,7 +24,8 @@ inline void tc_trace_report(const DeviceInfo& dev, int grid) {
     cudaDeviceSynchronize();
     std::vector<long long> host((size_t)dev.sms * kTraceWarps * kTraceSlots);
     cudaMemcpy(host.data(), buf, host.size() * sizeof(long long), cudaMemcpyDeviceToHost);
-    const char* role[kTraceWarps] = {"F0", "I1", "F2", "I3", "F4", "I5", "F6", "I7", "X8", "X9", "X10", "X11", "PROD", "MMA", "O14", "O15"};
+    const char* role[kTraceWarps] = {"F0", "I1", "F2", "I3", "F4", "I5", "F6", "I7", "F8", "I9", "F10", "I11", "F12", "I13", "F14", "I15",
+                                     "X16", "X17", "X18", "X19", "PROD", "MMA", "-", "-"};
     for (int w = 0; w < kTraceWarps; ++w) {
         double t[kTraceSlots] = {};
         for (int b = 0; b < grid; ++b)
