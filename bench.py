@@ -50,12 +50,14 @@ def hbm_peak():
 
 
 def traffic_per_row():
-    """DRAM bytes (read + write) per signal row of the fused kernel, from the committed ncu
-    capture (profiles/traffic.json); traffic grows in proportion to the rows a launch processes."""
+    """DRAM bytes READ per signal row of the fused kernel, from the committed ncu capture
+    (profiles/traffic.json); read traffic grows in proportion to the rows a launch processes.  The
+    capture cannot count the write side: a launch ends with up to an L2's worth (126 MB) of freshly
+    written output lines still on chip."""
     p = os.path.join(ROOT, "profiles", "traffic.json")
     try:
         with open(p) as f:
-            return json.load(f).get("fused_1d_dy256_k64_n64_dram_bytes_per_row")
+            return json.load(f).get("fused_1d_dy256_k64_n64_dram_read_bytes_per_row")
     except Exception:
         return None
 
@@ -134,37 +136,79 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # CPU arm: the oracle port, all host threads, bounded sample of the same workload
 # ------------------------------------------------------------------------------------------------
+def _cpu_threads():
+    # all host threads this process may use (torchrun exports OMP_NUM_THREADS=1, which would
+    # otherwise turn the CPU arm into a single-thread run)
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def _cpu_layer_scipy(x, ws, threads):
+    """The same layer with scipy's pocketfft (all threads) and numpy's BLAS matmul."""
+    import numpy as np
+    import scipy.fft
+
+    X = scipy.fft.fft(x, axis=-1, workers=threads)[..., :64]                       # [rows, K, 64]
+    Y = np.matmul(np.swapaxes(X, 1, 2), ws)                                        # [rows, 64, N]
+    Yp = np.zeros((x.shape[0], ws.shape[1], x.shape[2]), dtype=np.complex64)
+    Yp[..., :64] = np.swapaxes(Y, 1, 2)
+    return scipy.fft.ifft(Yp, axis=-1, workers=threads)
+
+
 def time_cpu_port(steps, warmup, budget_s=20.0):
+    """CPU arm: a bounded sample of the workload on all host threads.  Two implementations of the
+    same math are tried on a probe -- the float C port of the path (oracle/spectral_oracle.c,
+    OpenMP) and scipy.fft + numpy.matmul -- and the faster one is timed.  A measurement is `steps`
+    passes; measurements repeat until two in a row agree within 10 % (at most six) and the best is
+    reported, because host timings on a shared box wander."""
     import numpy as np
     from oracle import oracle_c
 
     w = WORKLOAD
-    # all host threads this process may use (torchrun exports OMP_NUM_THREADS=1, which would
-    # otherwise turn the CPU arm into a single-thread run)
-    try:
-        threads = len(os.sched_getaffinity(0))
-    except AttributeError:
-        threads = os.cpu_count() or 1
+    threads = _cpu_threads()
     rng = np.random.default_rng(1234)
     probe = 128
     xs = (rng.uniform(-1, 1, (probe, w["K"], w["DY"])) + 1j * rng.uniform(-1, 1, (probe, w["K"], w["DY"]))).astype(np.complex64)
     ws = ((rng.standard_normal((w["K"], w["N"])) + 1j * rng.standard_normal((w["K"], w["N"]))) / np.sqrt(w["K"])).astype(np.complex64)
-    oracle_c.spectral_conv_1d(xs, ws, double=False, threads=threads)  # load + first touch
-    t0 = time.perf_counter()
-    oracle_c.spectral_conv_1d(xs, ws, double=False, threads=threads)
-    per_row = (time.perf_counter() - t0) / probe
-    total_iters = max(1, steps + warmup)
-    rows = int(max(probe, min(w["bs"], budget_s / total_iters / max(per_row, 1e-9))))
+    impls = {"port": lambda x: oracle_c.spectral_conv_1d(x, ws, double=False, threads=threads)}
+    try:
+        import scipy.fft  # noqa: F401
+
+        impls["scipy"] = lambda x: _cpu_layer_scipy(x, ws, threads)
+    except Exception:
+        pass
+    per_row = {}
+    for name, fn in impls.items():
+        fn(xs)                                                  # load + first touch
+        best = float("inf")
+        for _ in range(3):                                      # best of three: one slow probe must not pick the wrong arm
+            t0 = time.perf_counter()
+            fn(xs)
+            best = min(best, time.perf_counter() - t0)
+        per_row[name] = best / probe
+    kind = min(per_row, key=per_row.get)
+    fn = impls[kind]
+    total_iters = max(1, 3 * steps + warmup)                    # room for three measurements in the budget
+    rows = int(max(probe, min(w["bs"], budget_s / total_iters / max(per_row[kind], 1e-9))))
     rows -= rows % 64 if rows >= 64 else 0
     x = (rng.uniform(-1, 1, (rows, w["K"], w["DY"])) + 1j * rng.uniform(-1, 1, (rows, w["K"], w["DY"]))).astype(np.complex64)
     for _ in range(warmup):
-        oracle_c.spectral_conv_1d(x, ws, double=False, threads=threads)
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        oracle_c.spectral_conv_1d(x, ws, double=False, threads=threads)
-    dt = (time.perf_counter() - t0) / max(steps, 1)
+        fn(x)
+    times = []
+    for rep in range(6):
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            fn(x)
+        times.append((time.perf_counter() - t0) / max(steps, 1))
+        if len(times) >= 2 and abs(times[-1] - times[-2]) <= 0.1 * min(times[-1], times[-2]):
+            break
+    dt = min(times)
     layers_per_s = (rows / w["bs"]) / dt
-    sample = "%d of %d signal rows per step (float32 C port of the path, OpenMP), scaled linearly to the full batch" % (rows, w["bs"])
+    what = "float32 C port of the path, OpenMP" if kind == "port" else "scipy.fft (pocketfft) + numpy.matmul"
+    sample = "%d of %d signal rows per step (%s), scaled linearly to the full batch; best of %d measurements, probe s/row: %s" % (
+        rows, w["bs"], what, len(times), ", ".join("%s %.2e" % kv for kv in sorted(per_row.items())))
     return layers_per_s, dt * 1e3, threads, sample
 
 
@@ -179,7 +223,7 @@ def run_reference_arm(args, rank, world):
         "config": {"workload": WORKLOAD_NAME, **WORKLOAD},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "note": "the reference has no CPU implementation of this path; this times the CPU port (oracle/spectral_oracle.c)",
+        "note": "the reference has no CPU implementation of this path; this times the faster of the CPU port (oracle/spectral_oracle.c) and scipy.fft + numpy.matmul (cpu_baseline.sample says which)",
     }
     print(json.dumps(line), flush=True)
 
@@ -204,46 +248,50 @@ def time_reference_gpu_variant_e(w):
     return None
 
 
-def time_2d_configs(t, dev):
-    """Not bench lines: the 2D parity configurations of BASELINE.json timed once for context
-    (variant D = image FFT, CGEMM, image iFFT; variant E = cuFFT + cuBLAS)."""
+def time_2d_config(t, dev, name, bs, K, N, D, layers, variants=("D", "E"), reps=3):
+    """One 2D parity configuration of BASELINE.json timed for context (not the bench line):
+    variant D = image FFT, CGEMM, image iFFT; variant E = cuFFT + cuBLAS.  `layers` chained layers
+    ping-pong two buffers.  Returns ms per layer of this process's `bs` batch items."""
     import torch
 
+    g = torch.Generator(device=dev).manual_seed(7)
+    a = torch.empty((K, bs, D, D), dtype=torch.complex64, device=dev)
+    for k in range(K):
+        a[k] = torch.view_as_complex(torch.rand((bs, D, D, 2), device=dev, generator=g) * 2 - 1)
+    b = torch.empty((N, bs, D, D), dtype=torch.complex64, device=dev)
+    ws = [torch.view_as_complex(torch.randn((N, K, 2), device=dev, generator=g) / (K ** 0.5)) for _ in range(layers)]
+    res = {}
+    for variant in variants:
+        plan = t.SpectralConv(2, bs, D, K, N, DX=D, variant=variant)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for it in range(reps + 1):
+            if it == 1:
+                e0.record()
+            src, dst = a, b
+            for l in range(layers):
+                plan(src, ws[l], y=dst)
+                if K == N:
+                    src, dst = dst, src
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps / layers
+        res[variant] = {"ms_per_layer": ms, "algorithmic_GBps": 8 * bs * D * D * (K + N) / ms * 1e-6, "kernels": plan.kernels()}
+        plan.close()
+        del plan
+    del a, b
+    torch.cuda.empty_cache()
+    return res
+
+
+def time_2d_configs(t, dev):
     out = {}
     for name, bs, K, N, D, layers in (("config2_2d_bs16_k32_n64_256x256", 16, 32, 64, 256, 1),
                                       ("config4_2d_bs256_k64_n64_256x256_4_layers", 256, 64, 64, 256, 4)):
         try:
-            g = torch.Generator(device=dev).manual_seed(7)
-            a = torch.empty((K, bs, D, D), dtype=torch.complex64, device=dev)
-            for k in range(K):
-                a[k] = torch.view_as_complex(torch.rand((bs, D, D, 2), device=dev, generator=g) * 2 - 1)
-            b = torch.empty((N, bs, D, D), dtype=torch.complex64, device=dev)
-            ws = [torch.view_as_complex(torch.randn((N, K, 2), device=dev, generator=g) / (K ** 0.5)) for _ in range(layers)]
-            res = {}
-            for variant in ("D", "E"):
-                plan = t.SpectralConv(2, bs, D, K, N, DX=D, variant=variant)
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                reps = 3
-                for it in range(reps + 1):
-                    if it == 1:
-                        e0.record()
-                    src, dst = a, b
-                    for l in range(layers):
-                        plan(src, ws[l], y=dst)
-                        if K == N:
-                            src, dst = dst, src
-                e1.record()
-                torch.cuda.synchronize()
-                ms = e0.elapsed_time(e1) / reps / layers
-                bytes_layer = 8 * bs * D * D * (K + N)
-                res[variant] = {"ms_per_layer": ms, "algorithmic_GBps": bytes_layer / ms * 1e-6}
-                plan.close()
-                del plan
+            res = time_2d_config(t, dev, name, bs, K, N, D, layers)
             peak, _ = hbm_peak()
             res["D_frac_of_hbm_peak"] = res["D"]["algorithmic_GBps"] / peak
             out[name] = res
-            del a, b
-            torch.cuda.empty_cache()
         except Exception as e:      # context only: never fail the bench line over it
             out[name] = {"error": str(e)[:200]}
     return out
@@ -320,7 +368,16 @@ def run_gpu_arm(args, rank, world, local_rank):
     for _ in range(e2e_steps):
         plan.exec_host(xh, wh, yh)
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / e2e_steps
-    e2e_check = float((yh[:, :4].to(dev) - ys[0][:, :4]).abs().max()) if ring > 0 and args.warmup + args.steps > 0 else None
+    # the whole host-path output against the device path on the same input (every chunk, the tail included)
+    plan(xs[0], wt, y=ys[0])
+    torch.cuda.synchronize()
+    e2e_check = 0.0
+    for n0 in range(0, N, 8):
+        e2e_check = max(e2e_check, float((yh[n0:n0 + 8].to(dev) - ys[0][n0:n0 + 8]).abs().max()))
+    # no kernel-side wait may have run out anywhere above (read once, outside every timed region)
+    status_word = t.Handle.get(local_rank).device_status
+    if status_word != 0:
+        raise SystemExit("bench.py: device status word is %d: a kernel-side wait ran out, results are incomplete" % status_word)
 
     # For context at N > 1: the same kernel with the per-GPU work of the N = 1 run (every rank a
     # whole bs = 8192 batch, "weak" scaling).  The headline stays the sharded run above, which is
@@ -349,6 +406,26 @@ def run_gpu_arm(args, rank, world, local_rank):
         plan_full.close()
         del xf, yf
 
+    # BASELINE config 4 (2D, bs=256, K=N=64, 256x256, four chained layers), batch-sharded like the
+    # headline workload: every rank runs its bs/world slice; context number at every N.
+    sharded_2d = None
+    if not args.no_extras:
+        try:
+            if world == 1:
+                del xs, ys
+                xs = ys = None
+                torch.cuda.empty_cache()
+            lo4, hi4 = shard(256, world, rank)
+            barrier()
+            r4 = time_2d_config(t, dev, "config4", hi4 - lo4, 64, 64, 256, 4, variants=("D",))
+            ms4 = max_over_ranks(r4["D"]["ms_per_layer"])
+            barrier()
+            sharded_2d = {"ms_per_layer": ms4, "layers_per_s": 1000.0 / ms4, "bs_per_gpu": hi4 - lo4,
+                          "aggregate_algorithmic_GBps": 8 * 256 * 256 * 256 * 128 / ms4 * 1e-6, "kernels": r4["D"]["kernels"],
+                          "what": "2D bs=256 K=N=64 256x256, 4 chained layers, contiguous bs/world slice per GPU, max over ranks"}
+        except Exception as e:
+            sharded_2d = {"error": str(e)[:200]}
+
     if rank == 0:
         peak, peak_src = hbm_peak()
         achieved = step_bytes / (ms_local / args.steps * 1e-3) / 1e9
@@ -361,8 +438,10 @@ def run_gpu_arm(args, rank, world, local_rank):
                        "l2": "ring of %d input/output buffer pairs (%.0f MB per step per GPU), each larger than L2 in total" % (ring, step_bytes / 1e6)},
             "aggregate_algorithmic_GBps": algorithmic_bytes(w["bs"], w["dimX"], DY, K, N) / (ms_per_step * 1e-3) / 1e9,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": (tr * rows_local) if tr else None, "peak_source": peak_src,
-                         "kernel": "tfno::tc::spectral_tc_kernel<4,true> (tcgen05 fused FFT+CGEMM+iFFT)", "algorithmic_bytes_per_launch": step_bytes},
+                         "traffic": (tr * rows_local) if tr else None,
+                         "traffic_kind": "DRAM bytes read per launch (ncu at bs=1024, scaled by rows); the write side cannot be captured: up to an L2 of output is still on chip when a launch ends",
+                         "peak_source": peak_src, "kernel": "tfno::tc::spectral_tc_kernel<8,true> (tcgen05 fused FFT+CGEMM+iFFT): " + ";".join(plan.kernels()),
+                         "algorithmic_bytes_per_launch": step_bytes, "algorithmic_read_bytes_per_launch": step_bytes * K // (K + N)},
             "e2e": {"value": 1000.0 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 8 * (w["bs"] * w["dimX"] * DY * K + K * N * world),
                     "d2h_bytes_per_step": 8 * w["bs"] * w["dimX"] * DY * N, "max_abs_diff_vs_device_path": e2e_check},
@@ -371,12 +450,17 @@ def run_gpu_arm(args, rank, world, local_rank):
         }
         if weak is not None:
             line["weak_scaling"] = weak
+        if sharded_2d is not None:
+            line["config4_2d_sharded"] = sharded_2d
         if world == 1:
             v, ms, threads, sample = time_cpu_port(3, 1, budget_s=15.0)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
             ref_ms = time_reference_gpu_variant_e(w)
             line["reference_gpu"] = {"variant_E_as_shipped_ms": ref_ms,
                                      "what": "the reference's own TurboFNO_1D_E (cuFFT+cuBLAS, host sync after every kernel) built from its sources, same GPU"}
+            if xs is None:
+                xs = [torch.view_as_complex(torch.rand((K, rows_local, DY, 2), device=dev, generator=g) * 2 - 1) for _ in range(ring)]
+                ys = [torch.empty((N, rows_local, DY), dtype=torch.complex64, device=dev) for _ in range(ring)]
             pe = t.SpectralConv(1, bs_local, DY, K, N, dimX=w["dimX"], variant="E")
             for i in range(3):
                 pe(xs[i % ring], wt, y=ys[i % ring])
