@@ -191,7 +191,28 @@ inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream
 #ifdef TFNO_TC_TRACE
     q.trace = tc_trace_buffer(dev, true);
 #endif
+#ifndef TFNO_NO_PDL
+    {
+        // launched so that its set-up may overlap the tail of the previous kernel in the stream
+        // (the kernel orders itself behind that kernel with griddepcontrol.wait)
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3(tc::kTcThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, kernel, q) != cudaSuccess) {
+            cudaGetLastError();
+            return TFNO_ERR_CUDA;
+        }
+    }
+#else
     kernel<<<(unsigned)grid, tc::kTcThreads, smem, st>>>(q);
+#endif
 #ifdef TFNO_TC_TRACE
     tc_trace_report(dev, (int)grid);
 #endif

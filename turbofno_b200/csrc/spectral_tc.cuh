@@ -327,6 +327,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
     const uint32_t tmem = *tmem_slot;
     const uint32_t TM_WHI = 0, TM_WLO = 2 * K, TM_ACC = 4 * K;        // column offsets; accumulators 2 x 64 columns
 
+#ifndef TFNO_NO_PDL
+    // Programmatic dependent launch: everything above touched only this CTA's shared and tensor
+    // memory, so it may run while the previous kernel of the stream is still finishing on other
+    // SMs.  From here on global memory is read and written: wait for the previous kernel to
+    // complete, then let the next launch begin its own set-up as SMs become free.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
     const long long first = blockIdx.x;
     const int n_it = first < p.rows ? (int)((p.rows - first + gridDim.x - 1) / gridDim.x) : 0;
     const long long n_loads = (long long)n_it * NC;
@@ -339,13 +347,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
         return NC == 1 ? (uint32_t)(it >> 1) : (uint32_t)it * (uint32_t)((NC - (c & 1) + 1) / 2) + (uint32_t)(c >> 1);
     };
 
-    // weights into tensor memory: thread i of warps 16-19 owns row i: rows 0-63 produce Re, rows
-    // 64-127 produce Im of output channel n = i & 63.  Column kk of a chunk = 2 * channel + part:
-    // Re and Im of a channel are adjacent, matching the 8-byte stores of the forward warps.
-    if (is_xfer) {
-        const int i = tid - 512, n = i & 63, im_row = i >> 6;
-        const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        for (int k0 = 0; k0 < K; k0 += 4) {
+    // Weights into tensor memory.  Lane l of a warp with warp % 4 == q reaches TMEM row i = 32 q + l:
+    // rows 0-63 produce Re, rows 64-127 produce Im of output channel n = i & 63.  All 24 warps take
+    // part (six per quarter, each a sixth of the channels), so that the set-up of a short launch
+    // stays short.  Column kk of a chunk = 2 * channel + part: Re and Im of a channel are adjacent,
+    // matching the 8-byte stores of the forward warps.
+    {
+        const int q = warp & 3, share = warp >> 2;                    // share 0..5 of quarter q
+        const int i = 32 * q + lane, n = i & 63, im_row = i >> 6;
+        const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16);
+        for (int k0 = 4 * share; k0 < K; k0 += 4 * (kTcThreads / 128)) {
             uint32_t hi[8], lo[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
