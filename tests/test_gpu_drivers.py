@@ -94,7 +94,10 @@ def test_plan_reports_the_kernels_it_launches(cuda):
     assert kernels(1, 1, 128, 8, 64) == ["spectral_tile_kernel<2,1,1,1>"]
     assert kernels(1, 5, 256, 32, 128) == ["spectral_tile_kernel<4,1,1,2>"]
     assert kernels(1, 300, 256, 128, 64) == ["spectral_tile_kernel<4,1,1,1>"]
-    assert kernels(1, 3, 512, 16, 64) == ["spectral_tile_kernel<8,1,1,1>"]
+    assert kernels(1, 3, 512, 128, 64) == ["spectral_tile_kernel<8,1,1,1>"]
+    # long transforms run the fused tensor-core kernel too (chunks of 8 and 4 channels)
+    assert kernels(1, 3, 512, 16, 64) == ["spectral_tc_kernel<16,1>"]
+    assert kernels(1, 300, 1024, 24, 64) == ["spectral_tc_kernel<32,1>"]
     # variant A: transform, tensor-core contraction (N = 64, K % 16 == 0, beta = 0), transform
     assert kernels(1, 300, 256, 64, 64, "A") == ["fft_rows_trunc_kernel<4>", "cgemm_tc_kernel<128>", "ifft_rows_pad_kernel<4>"]
     assert kernels(1, 300, 256, 64, 64, "A", beta=1j)[1] == "spectral_tile_kernel<2,0,0,1>"

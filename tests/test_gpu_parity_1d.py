@@ -111,10 +111,17 @@ def test_wide_channels(cuda):
         assert_close(run_1d(cuda, x, w, v), ref, "K=128 N=192 variant " + v)
 
 
-@pytest.mark.parametrize("DY,K", [(256, 16), (256, 32), (256, 48), (256, 64), (128, 32), (128, 64)])
+@pytest.mark.parametrize("DY,K", [(256, 16), (256, 32), (256, 48), (256, 64), (256, 96), (128, 32), (128, 64), (128, 96),
+                                  (512, 8), (512, 40), (512, 64), (1024, 24), (1024, 64)])
 def test_fused_kernel_chunk_counts_many_rows_per_sm(cuda, DY, K):
-    """One, two, three and four chunks of channels per row (three run on the FP32 kernel), with
-    three to four rows per SM so that every ring stage, S buffer and accumulator buffer is reused."""
+    """One to sixteen chunks of channels per row, even and odd counts, at every transform length of
+    the fused tensor-core kernel, with three to four rows per SM so that every ring stage, S buffer
+    and accumulator buffer is reused."""
+    import turbofno_b200 as t
+
+    probe = t.SpectralConv(1, 449, DY, K, 64, variant="D")
+    assert probe.kernels() == ["spectral_tc_kernel<%d,1>" % (DY // 32)]
+    probe.close()
     B, N = 449, 64
     x, w = oracle_np.make_inputs_1d(B, K, N, DY, seed=DY + K)
     assert_close(run_1d(cuda, x, w, "D"), oracle_c.spectral_conv_1d(x, w), "fused, %d channels at DY=%d" % (K, DY))

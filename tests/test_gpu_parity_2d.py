@@ -137,3 +137,24 @@ def test_centered_x_modes(cuda, DX, DY):
     with pytest.raises(t.TfnoError) as e:
         t.SpectralConv(2, bs, DY, K, N, DX=DX, variant="A", x_modes_centered=True)
     assert e.value.status == _lib.ERR_UNSUPPORTED
+
+
+def test_variant_D_ignores_beta_on_an_uninitialised_workspace(cuda):
+    """beta belongs to the variants that keep a spectrum C the caller can pre-load (A, B, C, E); the
+    2D variant D uses C as scratch, so a non-zero beta must not mix whatever the workspace holds
+    into the result (the 1D fused kernel has no C at all)."""
+    import torch
+    import turbofno_b200 as t
+
+    bs, K, N, DX, DY = 2, 16, 64, 128, 128
+    x, w = oracle_np.make_inputs_2d(bs, K, N, DX, DY, seed=5)
+    ref = oracle_c.spectral_conv_2d(x, w)
+    xd = torch.from_numpy(to_reference_layout(x)).to(cuda)
+    wd = torch.from_numpy(w_reference_layout(w)).to(cuda)
+    for beta in (0.0, -1.0 + 1.0j):
+        plan = t.SpectralConv(2, bs, DY, K, N, DX=DX, variant="D", beta=beta)
+        ws = torch.full((plan.workspace_bytes // 4,), float("nan"), dtype=torch.float32, device=cuda).view(torch.uint8)
+        y = plan(xd, wd, workspace=ws)
+        torch.cuda.synchronize()
+        assert_close(from_reference_layout(y.cpu().numpy()), ref, "2D variant D, beta=%s, NaN workspace" % (beta,))
+        plan.close()

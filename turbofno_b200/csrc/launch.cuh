@@ -148,11 +148,11 @@ inline int launch_tile_r(const DeviceInfo& dev, int R, const TileParams& p, cuda
 }
 
 // Tensor-core fused kernel: N a multiple of 64 (64 per launch), K a multiple of the chunk size
-// (16 channels at DY = 256, 32 at DY = 128) up to 96 (tensor memory holds the weights, 4K columns,
-// next to two accumulators), transform length 128 or 256.
+// (4096 / DY channels: 32, 16, 8, 4 at DY = 128, 256, 512, 1024) up to 96 (tensor memory holds the
+// weights, 4K columns, next to two accumulators), transform length 128 to 1024.
 inline bool tc_eligible(const DeviceInfo& dev, int len, const TileParams& p) {
     if (!dev.use_tensor_cores || !dev.status) return false;
-    if (p.N % 64 != 0 || (len != 128 && len != 256)) return false;
+    if (p.N % 64 != 0 || !supported_len(len)) return false;
     // N > 64 takes one launch per 64 output channels: worth it only when the launches are long
     if (p.N > 64 && p.rows < 2LL * dev.sms) return false;
     const int CH = 128 / (len / 32);
@@ -271,9 +271,13 @@ inline int launch_tile(const DeviceInfo& dev, int len, TileParams p, cudaStream_
                 q.N = 64;
                 q.w = p.w + (long long)n0 * p.w_stride_n;
                 q.y = p.y + (long long)n0 * p.y_stride_n;
-                int rc;
-                if (q.conj_inverse) rc = len == 128 ? launch_tc_inst<4, true>(dev, q, st) : launch_tc_inst<8, true>(dev, q, st);
-                else rc = len == 128 ? launch_tc_inst<4, false>(dev, q, st) : launch_tc_inst<8, false>(dev, q, st);
+                int rc = TFNO_ERR_UNSUPPORTED;
+                switch (len / 32) {            // lanes per signal
+                    case 4: rc = q.conj_inverse ? launch_tc_inst<4, true>(dev, q, st) : launch_tc_inst<4, false>(dev, q, st); break;
+                    case 8: rc = q.conj_inverse ? launch_tc_inst<8, true>(dev, q, st) : launch_tc_inst<8, false>(dev, q, st); break;
+                    case 16: rc = q.conj_inverse ? launch_tc_inst<16, true>(dev, q, st) : launch_tc_inst<16, false>(dev, q, st); break;
+                    case 32: rc = q.conj_inverse ? launch_tc_inst<32, true>(dev, q, st) : launch_tc_inst<32, false>(dev, q, st); break;
+                }
                 if (rc != TFNO_OK) return rc;
             }
             return TFNO_OK;

@@ -2,7 +2,7 @@
 // tensor cores (tcgen05 + TMEM) and bulk-copy (TMA engine) staging of input and output rows.
 // Same operator as spectral_tile_kernel<R,true,true,1>
 // (fusion_variants/1D_D_exp_fused_fft_cgemm_ifft/fused_fft_cgemm_ifft_7.cuh:9-222 in the
-// reference), restricted to N = 64 output channels, K <= 96, DY in {128, 256}.
+// reference), restricted to N = 64 output channels, K <= 96, DY in {128, 256, 512, 1024}.
 //
 // One persistent CTA per SM, 768 threads in six warpgroups.  The transforms run on the 32-point
 // register FFT (fft32.cuh): a signal is spread over R = DY/32 lanes, a thread holds 32 samples, so
@@ -120,8 +120,8 @@ template <int R> struct Geometry {
     static constexpr int STAGE_BYTES = CH * ROW_STRIDE;
     static constexpr int KSTEPS_PER_CHUNK = 2 * CH / 8;
     // Output rows are staged in shared memory and leave through the bulk-copy engine when there is
-    // room (DY = 256); at DY = 128 the S buffers are twice as large and the lanes store directly.
-    static constexpr bool STAGED_OUT = (R == 8);
+    // room (DY >= 256); at DY = 128 the S buffers are twice as large and the lanes store directly.
+    static constexpr bool STAGED_OUT = (R >= 8);
     static constexpr int OUT_ROWS = GPW;                    // output rows staged per inverse warp and task
     static constexpr int OUT_STRIDE = ROW_BYTES + 8 * R;    // padded like the input rows
     static constexpr int OUT_BYTES = STAGED_OUT ? OUT_ROWS * OUT_STRIDE : 0;   // per inverse warp
@@ -270,6 +270,7 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
 // R = DY / 32 lanes per signal.
 template <int R, bool INVERSE>
 __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) {
+    static_assert(R == 4 || R == 8 || R == 16 || R == 32, "DY = 32 R in {128, 256, 512, 1024}");
     using G = Geometry<R>;
     constexpr int CH = G::CH, GPW = G::GPW;
     extern __shared__ unsigned char smem_raw[];
@@ -574,6 +575,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 exchange_round1_32(v, R >> 1, coef);
                 exchange_round2_32(v, R >> 2);
                 if constexpr (R >= 8) exchange_round_32<8>(v, R >> 3, (r & (R >> 3)) != 0);
+                if constexpr (R >= 16) exchange_round_32<4>(v, R >> 4, (r & (R >> 4)) != 0);
+                if constexpr (R >= 32) exchange_round_32<2>(v, R >> 5, (r & (R >> 5)) != 0);
                 // lane r now holds modes 64/R*r + j, j < 64/R, in v[slot32(j)]
                 TFNO_TRACE_SINCE(8);
                 // this half-team's S buffer is free once the MMAs of its previous chunk have completed

@@ -193,6 +193,13 @@ int main(int argc, char** argv) {
         cudaFree(dx); cudaFree(dy); cudaFree(dw); cudaFree(dws);
         tfno_plan_destroy(plan);
     }
+    // a kernel-side wait that ran out leaves outputs incomplete without failing any call: read the
+    // device's status word once, after everything has been timed
+    int status_word = 0;
+    if (tfno_device_status(h, &status_word) != TFNO_OK || status_word != 0) {
+        fprintf(stderr, "%s: device status word %d after the run (a kernel-side wait ran out)\n", TFNO_TAG, status_word);
+        ++failures;
+    }
     tfno_destroy(h);
     return failures ? 1 : 0;
 }
