@@ -80,6 +80,14 @@ typedef struct {
                                  of the reference's corner 0..63
                                  (fusion_variants/2D_E_baseline/fused_trunc_2D.cu:30-39); Y modes
                                  stay 0..63.  0 = reference behaviour.                               */
+    long long w_stride_m;     /* 0: one K x N weight matrix shared by all modes, as in the reference
+                                 (fusion_variants/1D_E_baseline/cgemm.cuh:42-43).  Non-zero: per-mode
+                                 weights, what an FNO layer trains: element (k, n, m) at
+                                 k*w_stride_k + n*w_stride_n + m*w_stride_m, m = mode (1D) or
+                                 kx*64 + ky (2D).  With w_stride_k = w_stride_n = 0 the layout is
+                                 w[(n*K + k)*modes + m] (w_stride_m is then taken as 1).  Fast when
+                                 w_stride_m = 1.  1D variants A and D and the 2D variant D (all run
+                                 transform ; per-mode contraction ; transform), K <= 96, beta = 0.  */
 } tfno_problem;
 
 typedef struct tfno_handle_s tfno_handle;   /* one per device                                      */

@@ -25,6 +25,10 @@ fusion_variants/2D_E_baseline/fused_trunc_2D.cu:200-227), with FNO semantics
 Logical tensor shapes used by every oracle entry point (layout-independent):
   1D:  x[B, K, DY]        w[K, N]   ->  y[B, N, DY]        with B = bs*dimX
   2D:  x[B, K, DX, DY]    w[K, N]   ->  y[B, N, DX, DY]
+
+Per-mode weights (an extension, not reference behaviour: the reference's GEMM shares one K x N
+matrix between all modes, cgemm.cuh:42-43): w[K, N, modes] (1D) or w[K, N, modes, modes] (2D),
+C[b,n,m] = sum_k A[b,k,m] W[k,n,m].
 """
 import numpy as np
 
@@ -37,7 +41,7 @@ def spectral_conv_1d(x, w, modes=MODES, alpha=1.0, inverse=True, scale=True):
     B, K, DY = x.shape
     N = w.shape[1]
     X = np.fft.fft(x, axis=-1)[..., :modes]                  # [B,K,modes]
-    C = np.einsum("bkm,kn->bnm", X, w) * alpha               # [B,N,modes]
+    C = (np.einsum("bkm,knm->bnm", X, w) if w.ndim == 3 else np.einsum("bkm,kn->bnm", X, w)) * alpha   # [B,N,modes]
     P = np.zeros((B, N, DY), dtype=np.complex128)
     P[..., :modes] = C
     if inverse:
@@ -81,7 +85,7 @@ def spectral_conv_2d(x, w, modes=MODES, alpha=1.0, inverse=True, scale=True, x_m
     N = w.shape[1]
     kx = (np.arange(-modes // 2, modes // 2) % DX) if x_modes_centered else np.arange(modes)
     X = np.fft.fft2(x, axes=(-2, -1))[..., kx, :][..., :modes]   # [B,K,modes,modes]
-    C = np.einsum("bkxy,kn->bnxy", X, w) * alpha
+    C = (np.einsum("bkxy,knxy->bnxy", X, w) if w.ndim == 4 else np.einsum("bkxy,kn->bnxy", X, w)) * alpha
     P = np.zeros((B, N, DX, DY), dtype=np.complex128)
     P[..., kx, :modes] = C
     if inverse:
@@ -151,3 +155,11 @@ def errors(test, ref):
     den = max(np.abs(ref).max(), 1e-30)
     l2 = np.sqrt((d ** 2).sum()) / max(np.sqrt((np.abs(ref) ** 2).sum()), 1e-30)
     return float(d.max() / den), float(l2)
+
+
+def make_per_mode_weights(K, N, mode_shape, wseed=4321):
+    """w[K, N, *mode_shape], re/im ~ N(0, 1/K), seeded."""
+    rw = np.random.default_rng(wseed)
+    s = 1.0 / np.sqrt(K)
+    shape = (K, N) + tuple(mode_shape)
+    return (rw.normal(0, s, shape) + 1j * rw.normal(0, s, shape)).astype(np.complex64)

@@ -135,3 +135,20 @@ def test_centered_x_modes_keep_negative_frequencies():
     # a positive frequency inside both sets passes both
     x[0, 2] = np.exp(2j * np.pi * (9 * xx / DX + 3 * yy / DY))
     assert np.abs(oracle_np.spectral_conv_2d(x, w, x_modes_centered=True) - oracle_np.spectral_conv_2d(x, w)).max() < 1e-9
+
+
+def test_per_mode_weights_extension_of_the_oracle():
+    """Per-mode weights W[k,n,m]: with weights that do not depend on the mode the result is the
+    shared-weight layer; a weight tensor that is non-zero for one mode only passes that mode."""
+    x, w = oracle_np.make_inputs_1d(3, 8, 64, 128, seed=5)
+    wm = np.repeat(w[:, :, None], 64, axis=2)
+    assert np.abs(oracle_np.spectral_conv_1d(x, wm) - oracle_np.spectral_conv_1d(x, w)).max() < 1e-12
+    one = np.zeros((8, 64, 64), np.complex64)
+    one[2, 5, 9] = 3.0                      # channel 2 -> output 5, mode 9 only
+    y = oracle_np.spectral_conv_1d(x, one)
+    X = np.fft.fft(x.astype(np.complex128), axis=-1)
+    expect = 3.0 * X[:, 2, 9, None] * np.exp(2j * np.pi * 9 * np.arange(128) / 128) / 128
+    assert np.abs(y[:, 5] - expect).max() < 1e-12 and np.abs(np.delete(y, 5, axis=1)).max() < 1e-12
+    x2, w2 = oracle_np.make_inputs_2d(2, 8, 64, 128, 128, seed=6)
+    wm2 = np.broadcast_to(w2[:, :, None, None], (8, 64, 64, 64))
+    assert np.abs(oracle_np.spectral_conv_2d(x2, wm2) - oracle_np.spectral_conv_2d(x2, w2)).max() < 1e-12

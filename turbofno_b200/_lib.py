@@ -40,6 +40,7 @@ class Problem(ctypes.Structure):
         ("second_transform_forward", ctypes.c_int),
         ("scale_inverse", ctypes.c_int),
         ("x_modes_centered", ctypes.c_int),
+        ("w_stride_m", ctypes.c_longlong),
     ]
 
 

@@ -32,20 +32,22 @@ def _check_tensor(t, name):
         raise TypeError("%s must be a contiguous complex64 CUDA tensor" % name)
 
 
-def expected_shapes(rank, layout, B, K, N, DY, DX=None):
+def expected_shapes(rank, layout, B, K, N, DY, DX=None, per_mode=False):
     """Shapes (x, w, y) a plan accepts, from its problem alone.  Reference layout: x[K, B, ...],
-    w[N, K], y[N, B, ...]; batch-major: x[B, K, ...], w[K, N], y[B, N, ...]."""
+    w[N, K], y[N, B, ...]; batch-major: x[B, K, ...], w[K, N], y[B, N, ...].  Per-mode weights carry
+    the mode axes last: w[N, K, 64] / w[N, K, 64, 64] (batch-major: w[K, N, ...])."""
     tail = (DY,) if rank == 1 else (DX, DY)
+    wtail = () if not per_mode else ((64,) if rank == 1 else (64, 64))
     if layout == "reference":
-        return (K, B) + tail, (N, K), (N, B) + tail
-    return (B, K) + tail, (K, N), (B, N) + tail
+        return (K, B) + tail, (N, K) + wtail, (N, B) + tail
+    return (B, K) + tail, (K, N) + wtail, (B, N) + tail
 
 
-def check_shapes(rank, layout, B, K, N, DY, DX, x_shape, w_shape, y_shape=None):
+def check_shapes(rank, layout, B, K, N, DY, DX, x_shape, w_shape, y_shape=None, per_mode=False):
     """Raises ValueError unless the tensors have exactly the shapes the plan was made for.  The
     kernels trust the plan's sizes (bulk copies included): a smaller tensor would be read or
     written out of bounds on the device, so the mirror refuses it on the host."""
-    ex, ew, ey = expected_shapes(rank, layout, B, K, N, DY, DX)
+    ex, ew, ey = expected_shapes(rank, layout, B, K, N, DY, DX, per_mode)
     if tuple(x_shape) != ex:
         raise ValueError("x has shape %s, the plan needs %s" % (tuple(x_shape), ex))
     if tuple(w_shape) != ew:
@@ -104,11 +106,13 @@ class SpectralConv:
 
     variant: 'A'..'E' as in the TurboFNO_{1D,2D}_{A..E} executables.
     layout:  'reference' ([K][B][...], w[k + n*K]) or 'batch_major' ([B][K][...], w[K][N]).
+    per_mode_weights: w carries one K x N matrix per retained mode (mode axes last), as an FNO
+             layer trains them; the reference shares one matrix between all modes.
     """
 
     def __init__(self, rank, bs, DY, K, N, dimX=1, DX=None, variant="D", alpha=1.0 + 0j, beta=0j,
                  second_transform_forward=False, scale_inverse=True, layout="reference", device=None, modes=64,
-                 x_modes_centered=False):
+                 x_modes_centered=False, per_mode_weights=False):
         self.handle = Handle.get(device)
         self.lib = self.handle.lib
         p = Problem()
@@ -124,10 +128,14 @@ class SpectralConv:
         self.rank = rank
         self.B = bs * dimX if rank == 1 else bs
         unit = DY if rank == 1 else p.DX * DY
+        self.per_mode = bool(per_mode_weights)
+        nmodes = 64 if rank == 1 else 64 * 64
+        if self.per_mode:
+            p.w_stride_m = 1                # mode axes last and contiguous in both layouts
         if layout == "batch_major":
             p.x_stride_b, p.x_stride_k = K * unit, unit
             p.y_stride_b, p.y_stride_n = N * unit, unit
-            p.w_stride_k, p.w_stride_n = N, 1
+            p.w_stride_k, p.w_stride_n = (N * nmodes, nmodes) if self.per_mode else (N, 1)
         elif layout != "reference":
             raise ValueError("layout must be 'reference' or 'batch_major'")
         self.layout = layout
@@ -162,7 +170,7 @@ class SpectralConv:
 
     def _check_call(self, x, w, y, workspace):
         p = self.problem
-        check_shapes(self.rank, self.layout, self.B, p.K, p.N, p.DY, p.DX, x.shape, w.shape, None if y is None else y.shape)
+        check_shapes(self.rank, self.layout, self.B, p.K, p.N, p.DY, p.DX, x.shape, w.shape, None if y is None else y.shape, self.per_mode)
         dev = torch.device("cuda", self.handle.device)
         for name, t in (("x", x), ("w", w), ("y", y), ("workspace", workspace)):
             if t is not None and t.device != dev:
@@ -192,7 +200,7 @@ class SpectralConv:
             if t.is_cuda or t.dtype != torch.complex64 or not t.is_contiguous():
                 raise TypeError("exec_host needs contiguous complex64 host tensors")
         p = self.problem
-        check_shapes(self.rank, self.layout, self.B, p.K, p.N, p.DY, p.DX, x_host.shape, w_host.shape, y_host.shape)
+        check_shapes(self.rank, self.layout, self.B, p.K, p.N, p.DY, p.DX, x_host.shape, w_host.shape, y_host.shape, self.per_mode)
         check(self.lib.tfno_exec_host(self._plan, ctypes.c_void_p(x_host.data_ptr()), ctypes.c_void_p(w_host.data_ptr()),
                                       ctypes.c_void_p(y_host.data_ptr())), "tfno_exec_host")
         return y_host

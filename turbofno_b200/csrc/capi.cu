@@ -35,6 +35,7 @@ struct tfno_plan_s {
     long long B = 0;                    // 1D: bs*dimX rows; 2D: bs images per channel
     size_t ws_bytes = 0;
     bool default_layout = true;
+    bool per_mode = false;              // per-mode weights (w_stride_m != 0)
     // variant E
     cufftHandle fft_fwd = 0, fft_inv = 0;
     bool have_fft = false;
@@ -67,6 +68,12 @@ struct Workspace {
     size_t offA = 0, offC = 0, offT1 = 0, offT2 = 0, offF = 0, total = 0;
 };
 
+size_t weight_bytes(const tfno_plan_s& pl) {
+    const tfno_problem& p = pl.p;
+    const size_t nmodes = !pl.per_mode ? 1 : (p.rank == 1 ? (size_t)kModes : (size_t)kModes * kModes);
+    return sizeof(float2) * (size_t)p.K * p.N * nmodes;
+}
+
 Workspace carve(const tfno_plan_s& pl) {
     const tfno_problem& p = pl.p;
     Workspace w;
@@ -75,7 +82,8 @@ Workspace carve(const tfno_plan_s& pl) {
     const size_t szC = align_up(sizeof(float2) * (size_t)(p.N * pl.B * per_row));
     size_t off = 0;
     auto take = [&](size_t& slot, size_t sz) { slot = off; off += sz; };
-    const int v = p.variant;
+    int v = p.variant;
+    if (p.w_stride_m != 0 && p.rank == 1) v = TFNO_VARIANT_A;      // per-mode weights: three kernels, spectra A and C in the workspace
     if (p.rank == 1) {
         if (v == TFNO_VARIANT_A || v == TFNO_VARIANT_C || v == TFNO_VARIANT_E) take(w.offA, szA);
         if (v == TFNO_VARIANT_A || v == TFNO_VARIANT_B || v == TFNO_VARIANT_E) take(w.offC, szC);
@@ -104,6 +112,12 @@ int validate(const tfno_problem& p) {
     if (p.rank == 2 && p.variant == TFNO_VARIANT_D && (p.DX > 256 || p.DY > 256)) return TFNO_ERR_UNSUPPORTED;
     // centered X modes: the whole-image kernels of the 2D variant D, true inverse only
     if (p.x_modes_centered && (p.rank != 2 || p.variant != TFNO_VARIANT_D || p.second_transform_forward)) return TFNO_ERR_UNSUPPORTED;
+    if (p.w_stride_m != 0) {
+        // per-mode weights: transform ; per-mode contraction ; transform
+        const bool ok_variant = (p.rank == 1) ? (p.variant == TFNO_VARIANT_A || p.variant == TFNO_VARIANT_D) : (p.variant == TFNO_VARIANT_D);
+        if (!ok_variant || p.K > 96 || p.beta_re != 0.f || p.beta_im != 0.f) return TFNO_ERR_UNSUPPORTED;
+        if (p.rank == 2 && (p.DX > 256 || p.DY > 256)) return TFNO_ERR_UNSUPPORTED;
+    }
     return TFNO_OK;
 }
 
@@ -274,11 +288,15 @@ int tfno_plan_create(tfno_handle* h, const tfno_problem* problem, tfno_plan** ou
     tfno_problem& p = pl->p;
     pl->B = (p.rank == 1) ? p.bs * p.dimX : p.bs;
     const long long unit = (p.rank == 1) ? p.DY : image_elems(p);
+    const long long nmodes = (p.rank == 1) ? kModes : (long long)kModes * kModes;
+    pl->per_mode = p.w_stride_m != 0;
+    const bool w_default = pl->per_mode ? (p.w_stride_k == 0 || (p.w_stride_m == 1 && p.w_stride_k == nmodes && p.w_stride_n == p.K * nmodes))
+                                        : (p.w_stride_k == 0 || (p.w_stride_k == 1 && p.w_stride_n == p.K));
     pl->default_layout = (p.x_stride_b == 0 || (p.x_stride_b == unit && p.x_stride_k == pl->B * unit)) &&
-                         (p.y_stride_b == 0 || (p.y_stride_b == unit && p.y_stride_n == pl->B * unit)) &&
-                         (p.w_stride_k == 0 || (p.w_stride_k == 1 && p.w_stride_n == p.K));
+                         (p.y_stride_b == 0 || (p.y_stride_b == unit && p.y_stride_n == pl->B * unit)) && w_default;
     if (p.x_stride_b == 0) { p.x_stride_b = unit; p.x_stride_k = pl->B * unit; }
     if (p.y_stride_b == 0) { p.y_stride_b = unit; p.y_stride_n = pl->B * unit; }
+    if (pl->per_mode && p.w_stride_k == 0) { p.w_stride_m = 1; p.w_stride_k = nmodes; p.w_stride_n = p.K * nmodes; }
     if (p.w_stride_k == 0) { p.w_stride_k = 1; p.w_stride_n = p.K; }
     if ((p.x_stride_b | p.x_stride_k | p.y_stride_b | p.y_stride_n) & 1) {   // 16-byte alignment of rows
         delete pl;
@@ -357,6 +375,17 @@ static int exec_impl(const tfno_plan* plan, const DeviceInfo& dev, const void* x
         ir.nsig = p.N * B; ir.per_k = B; ir.in = C; ir.out = yout; ir.stride_row = p.y_stride_b; ir.stride_k = p.y_stride_n;
         ir.gain = f2(scale, 0.f); ir.conj_inverse = conj;
         t.rows = B;
+        if (plan->per_mode) {
+            rc = launch_fft_rows(dev, p.DY, fr, st);
+            if (rc) return rc;
+            PerModeParams pm{};
+            pm.rows = B; pm.modes = kModes; pm.K = p.K; pm.N = p.N;
+            pm.a = A; pm.w = win; pm.w_sk = p.w_stride_k; pm.w_sn = p.w_stride_n; pm.w_sm = p.w_stride_m;
+            pm.c = C; pm.alpha = alpha;
+            rc = launch_permode(dev, pm, st);
+            if (rc) return rc;
+            return launch_ifft_rows(dev, p.DY, ir, st);
+        }
         switch (p.variant) {
             case TFNO_VARIANT_A:
                 rc = launch_fft_rows(dev, p.DY, fr, st);
@@ -402,6 +431,17 @@ static int exec_impl(const tfno_plan* plan, const DeviceInfo& dev, const void* x
         ir.nsig = p.N * rows; ir.per_k = p.N * rows; ir.in = C; ir.out = T2; ir.stride_row = p.DY; ir.stride_k = 0;
         ir.gain = f2(1.f, 0.f); ir.conj_inverse = conj;
         t.rows = rows;
+        if (plan->per_mode) {
+            rc = launch_fft2d(dev, p.DX, p.DY, fi, false, st);
+            if (rc) return rc;
+            PerModeParams pm{};
+            pm.rows = B; pm.modes = (long long)kModes * kModes; pm.K = p.K; pm.N = p.N;
+            pm.a = A; pm.w = win; pm.w_sk = p.w_stride_k; pm.w_sn = p.w_stride_n; pm.w_sm = p.w_stride_m;
+            pm.c = C; pm.alpha = alpha;
+            rc = launch_permode(dev, pm, st);
+            if (rc) return rc;
+            return launch_fft2d(dev, p.DX, p.DY, ii, true, st);
+        }
         switch (p.variant) {
             case TFNO_VARIANT_D:
                 rc = launch_fft2d(dev, p.DX, p.DY, fi, false, st);
@@ -543,7 +583,7 @@ static int host_staging_init(tfno_plan_s* plan) {
         for (int i = 0; i < 2 && rc == TFNO_OK; ++i) {
             if (cudaMalloc(&hs.dx[i], xin) != cudaSuccess || cudaMalloc(&hs.dy[i], yout) != cudaSuccess ||
                 (wsz && cudaMalloc(&hs.dws[i], wsz) != cudaSuccess) ||
-                cudaMalloc(&hs.dw[i], sizeof(float2) * (size_t)p.K * p.N) != cudaSuccess ||
+                cudaMalloc(&hs.dw[i], weight_bytes(*plan)) != cudaSuccess ||
                 cudaStreamCreateWithFlags(&hs.stream[i], cudaStreamNonBlocking) != cudaSuccess) {
                 cudaGetLastError();
                 rc = TFNO_ERR_ALLOC;
@@ -594,7 +634,7 @@ int tfno_exec_host(tfno_plan* plan, const void* x_host, const void* w_host, void
         // each stream brings its own copy of the weights with its first chunk (stream-ordered
         // before that chunk's kernels; no host synchronisation, no ordering between the streams)
         if (chunk_index < 2 &&
-            cudaMemcpyAsync(hs.dw[slot], w_host, sizeof(float2) * (size_t)p.K * p.N, cudaMemcpyHostToDevice, st) != cudaSuccess)
+            cudaMemcpyAsync(hs.dw[slot], w_host, weight_bytes(*plan), cudaMemcpyHostToDevice, st) != cudaSuccess)
             return fail(TFNO_ERR_CUDA);
         // [K][bs][unit] on the host -> compact [K][nb][unit] on the device
         if (cudaMemcpy2DAsync(hs.dx[slot], width, static_cast<const char*>(x_host) + sizeof(float2) * (size_t)(unit * b0),

@@ -12,6 +12,7 @@
 #include "spectral_kernels.cuh"
 #include "spectral_tc.cuh"
 #include "cgemm_tc.cuh"
+#include "cgemm_permode.cuh"
 
 namespace tfno {
 
@@ -297,6 +298,28 @@ inline int launch_tile(const DeviceInfo& dev, int len, TileParams p, cudaStream_
         if (rc != TFNO_OK) return rc;
     }
     return TFNO_OK;
+}
+
+// Per-mode weights: persistent CTAs over (group of four modes, block of 64 outputs, split of the rows).
+inline int launch_permode(const DeviceInfo& dev, PerModeParams p, cudaStream_t st) {
+    if (p.rows <= 0) return TFNO_OK;
+    if (p.K <= 0 || p.N % kPmNB != 0 || p.modes % kPmModes != 0) return TFNO_ERR_UNSUPPORTED;
+    const size_t smem = pm_smem_bytes(p.K);
+    if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
+    if (record_launch(dev, "cgemm_permode_kernel")) return TFNO_OK;
+    int occ = 0;
+    int rc = prepare_kernel(cgemm_permode_kernel, smem, dev, &occ, kPmThreads);
+    if (rc != TFNO_OK) return rc;
+    // enough work items for two per SM, but never more splits than row tiles
+    const long long groups = p.modes / kPmModes, passes = p.N / kPmNB, tiles = (p.rows + kPmRowTile - 1) / kPmRowTile;
+    long long splits = (2LL * dev.sms + groups * passes - 1) / (groups * passes);
+    if (splits > tiles) splits = tiles;
+    if (splits < 1) splits = 1;
+    p.splits = (int)splits;
+    long long grid = groups * passes * splits;
+    if (grid > (long long)dev.sms * occ) grid = (long long)dev.sms * occ;
+    cgemm_permode_kernel<<<(unsigned)grid, kPmThreads, smem, st>>>(p);
+    return launch_status();
 }
 
 template <typename Params, typename Kernel>
