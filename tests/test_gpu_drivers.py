@@ -102,7 +102,8 @@ def test_plan_reports_the_kernels_it_launches(cuda):
     assert kernels(1, 300, 256, 64, 64, "A") == ["fft_rows_trunc_kernel<4>", "cgemm_tc_kernel<128>", "ifft_rows_pad_kernel<4>"]
     assert kernels(1, 300, 256, 64, 64, "A", beta=1j)[1] == "spectral_tile_kernel<2,0,0,1>"
     # 2D variant D
-    assert kernels(2, 16, 256, 32, 64, DX=256) == ["fft2d_trunc_kernel<4,4,paired,256>", "cgemm_tc_kernel<128>", "ifft2d_pad_kernel<4,4,paired,256>"]
+    assert kernels(2, 16, 256, 32, 64, DX=256) == ["fft2d_trunc32_kernel<8,8>", "cgemm_tc_kernel<128>", "ifft2d_pad_kernel<4,4,paired,256>"]
+    assert kernels(2, 16, 128, 32, 64, DX=256) == ["fft2d_trunc32_kernel<8,4>", "cgemm_tc_kernel<128>", "ifft2d_pad32_kernel<8,4,1>"]
     assert kernels(2, 1, 128, 8, 64, DX=128) == ["fft2d_trunc_kernel<2,2,paired,128>", "spectral_tile_kernel<2,0,0,1>", "ifft2d_pad_kernel<2,2,paired,128>"]
     # library path
     assert kernels(1, 4, 128, 8, 64, "E") == ["cufftExecC2C", "truncate_rows_kernel", "cublasCgemm", "zero_pad_rows_kernel", "cufftExecC2C"]

@@ -84,8 +84,11 @@ template <int R> TFNO_HD bool lane_rotated32(int r) { return (r & (R >> 2)) != 0
 
 // forward: twF[r][j] = t_r * W_DY^{r k},  k = (j + 16*rotated(r)) mod 32,  t_r = 1 for the lanes
 // r < R/2 (which keep modes < 32) and -W_R^{a} for r = a + R/2 (which keep modes 32..63).
+// `centered`: the kept modes are -32..31 instead of 0..63 (mode k of the result is k - 32 of the
+// signal): the transform of the signal times e^{+2 pi i 32 n / DY}, which for sample n = R*i + r is
+// the per-lane constant e^{+2 pi i r / R} = W_DY^{-32 r} -- it goes into the lane's row of the table.
 template <int R>
-TFNO_HD void fill_forward_table32(float2* twF, int tid, int nthreads) {
+TFNO_HD void fill_forward_table32(float2* twF, int tid, int nthreads, bool centered = false) {
     constexpr int DY = 32 * R;
     for (int i = tid; i < R * 32; i += nthreads) {
         const int r = i >> 5, j = i & 31;
@@ -93,6 +96,7 @@ TFNO_HD void fill_forward_table32(float2* twF, int tid, int nthreads) {
         int e = (r * k) & (DY - 1);
         const bool hi = r >= (R >> 1);
         if (hi) e = (e + 32 * (r - (R >> 1)) + DY / 2) & (DY - 1);      // times -W_R^{a} = W_DY^{32 a + DY/2}
+        if (centered) e = (e - 32 * r) & (DY - 1);
         twF[tw_index<R>(r, j)] = unit_root(e, DY, -1.0f);
     }
 }
@@ -121,12 +125,15 @@ TFNO_HD void fill_inverse_table32(float2* twI, int tid, int nthreads, float2 g, 
 // Folded form of the inverse table: W_DY^{-j1 (m'+32)} = W_DY^{-j1 m'} W_R^{-j1}, so
 //     C[m'] T[m'] + C[m'+32] T[m'+32] = T[m'] ( C[m'] + c C[m'+32] ),   c = inverse_fold_coef32(j1)
 // and a lane needs 32 table entries (m' < 32) plus one constant.
+// `centered` (true inverse only): the 64 given modes are -32..31; sample R*j2 + j1 of the result is
+// the ordinary one times e^{-2 pi i 32 (R*j2 + j1) / DY} = e^{-2 pi i j1 / R}, a per-lane constant.
 template <int R>
-TFNO_HD void fill_inverse_table32_folded(float2* twI, int tid, int nthreads, float2 g, bool conj) {
+TFNO_HD void fill_inverse_table32_folded(float2* twI, int tid, int nthreads, float2 g, bool conj, bool centered = false) {
     constexpr int DY = 32 * R;
     for (int i = tid; i < R * 32; i += nthreads) {
         const int j1 = i >> 5, m = i & 31;
-        twI[tw_index<R>(j1, m)] = cmul(g, unit_root((j1 * m) & (DY - 1), DY, conj ? 1.0f : -1.0f));
+        const int e = centered ? (j1 * m - 32 * j1) & (DY - 1) : (j1 * m) & (DY - 1);
+        twI[tw_index<R>(j1, m)] = cmul(g, unit_root(e, DY, conj ? 1.0f : -1.0f));
     }
 }
 template <int R>
