@@ -30,12 +30,18 @@ struct PerModeParams {
     float2* c;                         // C[(n*rows + b)*modes + m]
     float2 alpha;
     int splits;                        // row tiles of a mode group are dealt to this many CTAs
+    int stage_a;                       // 1: the A tile goes through shared memory
 };
 
 // weights of one mode in shared memory: [K][64] complex, plus 32 bytes so that the four modes a
 // warp reads in one instruction fall into different banks
 __host__ __device__ inline size_t pm_mode_stride_bytes(int K) { return (size_t)K * kPmNB * sizeof(float2) + 32; }
-inline size_t pm_smem_bytes(int K) { return kPmModes * pm_mode_stride_bytes(K); }
+// A tile of 32 rows x K channels x 4 modes, staged in shared memory when it fits next to the weights
+// (K <= 64): all 16 warps of a CTA read the same A values, and reading them from global memory
+// through L1 costs the load/store unit 2.4x what the arithmetic costs the FMA pipe.
+__host__ __device__ inline size_t pm_atile_bytes(int K) { return (size_t)K * kPmRowTile * kPmModes * sizeof(float2); }
+inline bool pm_stage_a(int K, int max_smem) { return (long long)(kPmModes * pm_mode_stride_bytes(K) + pm_atile_bytes(K)) <= max_smem; }
+inline size_t pm_smem_bytes(int K, bool stage_a) { return kPmModes * pm_mode_stride_bytes(K) + (stage_a ? pm_atile_bytes(K) : 0); }
 
 __global__ void __launch_bounds__(kPmThreads, 1) cgemm_permode_kernel(PerModeParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -64,6 +70,8 @@ __global__ void __launch_bounds__(kPmThreads, 1) cgemm_permode_kernel(PerModePar
         }
         __syncthreads();
         const float2* wj = reinterpret_cast<const float2*>(smem_raw + j * mode_stride) + 4 * nb;
+        // staged A tile: sA[k][r][rg][mode] (the 32 lanes of a warp read 256 contiguous bytes)
+        float2* sA = reinterpret_cast<float2*>(smem_raw + kPmModes * mode_stride);
         for (long long tile = split; tile < tiles; tile += p.splits) {
             const long long b0 = tile * kPmRowTile + 4 * rg;
             float2 acc[4][4];
@@ -75,6 +83,18 @@ __global__ void __launch_bounds__(kPmThreads, 1) cgemm_permode_kernel(PerModePar
             long long rowoff[4];
 #pragma unroll
             for (int r = 0; r < 4; ++r) rowoff[r] = ((b0 + r < p.rows) ? b0 + r : p.rows - 1) * p.modes + m0 + j;
+            if (p.stage_a) {
+                __syncthreads();                 // the previous tile is no longer read
+                // one 16-byte load = two modes of one (channel, row): 2 * 32 * K of them
+                for (int i = tid; i < 2 * kPmRowTile * p.K; i += kPmThreads) {
+                    const int half = i & 1, row = (i >> 1) & (kPmRowTile - 1), k = i >> 6;
+                    long long b = tile * kPmRowTile + row;
+                    if (b >= p.rows) b = p.rows - 1;
+                    const float4 q = __ldg(reinterpret_cast<const float4*>(p.a + ((long long)k * p.rows + b) * p.modes + m0) + half);
+                    *reinterpret_cast<float4*>(sA + (((size_t)k * 4 + (row & 3)) * 8 + (row >> 2)) * kPmModes + 2 * half) = q;
+                }
+                __syncthreads();
+            }
 #pragma unroll 4
             for (int k = 0; k < p.K; ++k) {
                 const float4 w01 = *reinterpret_cast<const float4*>(wj + (size_t)k * kPmNB);
@@ -83,7 +103,7 @@ __global__ void __launch_bounds__(kPmThreads, 1) cgemm_permode_kernel(PerModePar
                 const float2* ak = p.a + (long long)k * p.rows * p.modes;
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
-                    const float2 av = __ldg(ak + rowoff[r]);
+                    const float2 av = p.stage_a ? sA[(((size_t)k * 4 + r) * 8 + rg) * kPmModes + j] : __ldg(ak + rowoff[r]);
 #pragma unroll
                     for (int n = 0; n < 4; ++n) {
                         acc[r][n].x = fmaf(av.x, wv[n].x, fmaf(-av.y, wv[n].y, acc[r][n].x));

@@ -305,7 +305,8 @@ inline int launch_tile(const DeviceInfo& dev, int len, TileParams p, cudaStream_
 inline int launch_permode(const DeviceInfo& dev, PerModeParams p, cudaStream_t st) {
     if (p.rows <= 0) return TFNO_OK;
     if (p.K <= 0 || p.N % kPmNB != 0 || p.modes % kPmModes != 0) return TFNO_ERR_UNSUPPORTED;
-    const size_t smem = pm_smem_bytes(p.K);
+    p.stage_a = pm_stage_a(p.K, dev.max_smem_optin) && (p.modes % 2 == 0) ? 1 : 0;
+    const size_t smem = pm_smem_bytes(p.K, p.stage_a != 0);
     if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
     if (record_launch(dev, "cgemm_permode_kernel")) return TFNO_OK;
     int occ = 0;
