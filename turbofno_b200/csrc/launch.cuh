@@ -161,6 +161,40 @@ inline bool tc_eligible(const DeviceInfo& dev, int len, const TileParams& p) {
     return p.K >= CH && p.K <= 96 && p.K % CH == 0;
 }
 
+// cuTensorMapEncodeTiled of the installed driver, looked up through the runtime (the library does
+// not link libcuda); nullptr if the driver does not offer it.
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline TensorMapEncodeFn tensor_map_encoder() {
+    static TensorMapEncodeFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            f = nullptr;
+        }
+        return reinterpret_cast<TensorMapEncodeFn>(f);
+    }();
+    return fn;
+}
+
+// y as [channels][rows][len] complex (8-byte elements), box = {len, 1, box_channels}.  False when the
+// layout does not meet the encoder's rules (16-byte aligned base and strides, box at most 256 wide).
+inline bool encode_output_map(CUtensorMap* map, float2* y, int len, long long rows, int channels,
+                              long long stride_row, long long stride_n, int box_channels) {
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (!enc || len > 256 || rows <= 0 || rows > 0x7fffffffLL || (reinterpret_cast<uintptr_t>(y) & 15) != 0) return false;
+    if (stride_row <= 0 || stride_n <= 0 || (stride_row & 1) || (stride_n & 1)) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)len, (cuuint64_t)rows, (cuuint64_t)channels};
+    const cuuint64_t strides[2] = {(cuuint64_t)stride_row * 8, (cuuint64_t)stride_n * 8};
+    if (strides[0] >= (1ULL << 40) || strides[1] >= (1ULL << 40)) return false;
+    const cuuint32_t box[3] = {(cuuint32_t)len, 1u, (cuuint32_t)box_channels};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int R, bool INVERSE>
 inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
     auto kernel = tc::spectral_tc_kernel<R, INVERSE>;
@@ -188,6 +222,10 @@ inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream
     q.w = p.w; q.w_stride_k = p.w_stride_k; q.w_stride_n = p.w_stride_n;
     q.y = p.y; q.y_stride_row = p.y_stride_row; q.y_stride_n = p.y_stride_n;
     q.inv_gain = p.inv_gain; q.conj_inverse = p.conj_inverse; q.status = dev.status;
+#ifndef TFNO_NO_TENSOR_STORE
+    if constexpr (tc::Geometry<R>::TENSOR_OUT)
+        q.use_ymap = encode_output_map(&q.ymap, p.y, 32 * R, p.rows, 64, p.y_stride_row, p.y_stride_n, tc::Geometry<R>::GPW) ? 1 : 0;
+#endif
     long long grid = dev.sms;
     if (grid > p.rows) grid = p.rows;
 #ifdef TFNO_TC_TRACE

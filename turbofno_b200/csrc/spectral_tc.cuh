@@ -41,6 +41,7 @@
 // returns.
 #pragma once
 #include <cstdint>
+#include <cuda.h>          // CUtensorMap (types only: the encoder is fetched from the runtime)
 #include "fft32.cuh"
 
 namespace tfno {
@@ -91,6 +92,12 @@ struct TcParams {
     int conj_inverse;
     int* status;                // device-visible word; 0 = ok
     long long* trace;           // optional per-warp cycle counters (builds with TFNO_TC_TRACE only)
+    // Tiled view of y as [channel][row][DY] 8-byte elements, box = {DY, 1, channels of one inverse
+    // warp}: with it an inverse warp hands all its output rows of a task to the copy engine in ONE
+    // instruction instead of one per row (each costs the issuing warp ~175 cycles).  DY = 256 only
+    // (a box is at most 256 elements wide); 0 = not available, the rows leave one by one.
+    int use_ymap;
+    alignas(64) CUtensorMap ymap;
 };
 
 // SBO: bytes between 8-mode groups of the B operand S.  The contraction kernel of compact spectra
@@ -124,6 +131,7 @@ template <int R> struct Geometry {
     static constexpr bool STAGED_OUT = (R >= 8);
     static constexpr int OUT_ROWS = GPW;                    // output rows staged per inverse warp and task
     static constexpr int OUT_STRIDE = ROW_BYTES + 8 * R;    // padded like the input rows
+    static constexpr bool TENSOR_OUT = (R == 8);            // all rows of a task in one tiled copy
     static constexpr int OUT_BYTES = STAGED_OUT ? OUT_ROWS * OUT_STRIDE : 0;   // per inverse warp
 };
 
@@ -269,7 +277,7 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
 // roles run the same forward 32-point code); false: a second forward transform.
 // R = DY / 32 lanes per signal.
 template <int R, bool INVERSE>
-__global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) {
+__global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid_constant__ TcParams p) {
     static_assert(R == 4 || R == 8 || R == 16 || R == 32, "DY = 32 R in {128, 256, 512, 1024}");
     using G = Geometry<R>;
     constexpr int CH = G::CH, GPW = G::GPW;
@@ -353,24 +361,55 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
     // part (six per quarter, each a sixth of the channels), so that the set-up of a short launch
     // stays short.  Column kk of a chunk = 2 * channel + part: Re and Im of a channel are adjacent,
     // matching the 8-byte stores of the forward warps.
+    // The producer warp first starts the copies of the first ring stages, so that the input rows
+    // travel while the weights are being converted.
+    auto issue_load = [&](long long L) {       // whole producer warp; lanes < CH copy one row each
+        const int s = stage_of((int)(L / NC), (int)(L % NC));
+        const long long row = first + (L / NC) * gridDim.x;
+        const int c = (int)(L % NC);
+        if (lane == 0) mbar_arrive_expect_tx(bar(B_FULL + s), CH * G::ROW_BYTES);
+        __syncwarp();
+        for (int j = lane; j < CH; j += 32) {
+            const float2* src = p.x + row * p.x_stride_row + (long long)(c * CH + j) * p.x_stride_k;
+            bulk_load(smem_u32(ring + s * G::STAGE_BYTES + j * G::ROW_STRIDE), src, G::ROW_BYTES, bar(B_FULL + s));
+        }
+    };
+    long long preloaded = 0;
+    if (warp == kProducerWarp)
+        for (; preloaded < kStages && preloaded < n_loads; ++preloaded) issue_load(preloaded);
     {
         const int q = warp & 3, share = warp >> 2;                    // share 0..5 of quarter q
         const int i = 32 * q + lane, n = i & 63, im_row = i >> 6;
         const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16);
-        for (int k0 = 4 * share; k0 < K; k0 += 4 * (kTcThreads / 128)) {
-            uint32_t hi[8], lo[8];
+        // all loads of a thread first (K <= 96: at most four blocks of four channels), then the
+        // conversion: one trip to memory instead of one per block
+        constexpr int kMaxBlocks = 4;
+        float2 wv[kMaxBlocks][4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int k = k0 + (j >> 1), part = j & 1;
-                const float2 wv = __ldg(p.w + (long long)k * p.w_stride_k + (long long)n * p.w_stride_n);
-                // Re row: [ Wr | -Wi ],  Im row: [ Wi | Wr ]  against  S = [ Xr ; Xi ]
-                const float v = im_row ? (part ? wv.x : wv.y) : (part ? -wv.y : wv.x);
-                const float h = tf32_hi(v);
-                hi[j] = __float_as_uint(h);
-                lo[j] = __float_as_uint(tf32_hi(v - h));
+        for (int b = 0; b < kMaxBlocks; ++b) {
+            const int k0 = 4 * share + b * 4 * (kTcThreads / 128);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                wv[b][j] = (k0 < K) ? __ldg(p.w + (long long)(k0 + j) * p.w_stride_k + (long long)n * p.w_stride_n) : make_float2(0.f, 0.f);
+        }
+#pragma unroll
+        for (int b = 0; b < kMaxBlocks; ++b) {
+            const int k0 = 4 * share + b * 4 * (kTcThreads / 128);
+            if (k0 < K) {
+                uint32_t hi[8], lo[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int part = j & 1;
+                    const float2 w1 = wv[b][j >> 1];
+                    // Re row: [ Wr | -Wi ],  Im row: [ Wi | Wr ]  against  S = [ Xr ; Xi ]
+                    const float v = im_row ? (part ? w1.x : w1.y) : (part ? -w1.y : w1.x);
+                    const float h = tf32_hi(v);
+                    hi[j] = __float_as_uint(h);
+                    lo[j] = __float_as_uint(tf32_hi(v - h));
+                }
+                TFNO_TMEM_ST8(trow + TM_WHI + 2 * k0, hi);
+                TFNO_TMEM_ST8(trow + TM_WLO + 2 * k0, lo);
             }
-            TFNO_TMEM_ST8(trow + TM_WHI + 2 * k0, hi);
-            TFNO_TMEM_ST8(trow + TM_WLO + 2 * k0, lo);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     }
@@ -411,19 +450,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
             }
         } else if (warp == kProducerWarp) {
             // producer: keeps the ring full
-            auto issue_load = [&](long long L) {       // whole warp; lanes < CH copy one row each
-                const int s = stage_of((int)(L / NC), (int)(L % NC));
-                const long long row = first + (L / NC) * gridDim.x;
-                const int c = (int)(L % NC);
-                if (lane == 0) mbar_arrive_expect_tx(bar(B_FULL + s), CH * G::ROW_BYTES);
-                __syncwarp();
-                for (int j = lane; j < CH; j += 32) {
-                    const float2* src = p.x + row * p.x_stride_row + (long long)(c * CH + j) * p.x_stride_k;
-                    bulk_load(smem_u32(ring + s * G::STAGE_BYTES + j * G::ROW_STRIDE), src, G::ROW_BYTES, bar(B_FULL + s));
-                }
-            };
             bool ok = true;
-            long long L = 0;
+            long long L = preloaded;      // the first stages were started before the weights
             for (; L < n_loads && ok; ++L) {
                 const int s = stage_of((int)(L / NC), (int)(L % NC));
                 const uint32_t u = use_of((int)(L / NC), (int)(L % NC));
@@ -628,7 +656,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 if (lane < G::OUT_ROWS) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 __syncwarp();
                 TFNO_TRACE_SINCE(2);
-                float2* srow_out = reinterpret_cast<float2*>(ost + g * G::OUT_STRIDE);
+                // rows padded against bank conflicts, or dense as the tiled copy wants its box
+                const int out_stride = (G::TENSOR_OUT && p.use_ymap) ? G::ROW_BYTES : G::OUT_STRIDE;
+                float2* srow_out = reinterpret_cast<float2*>(ost + g * out_stride);
 #pragma unroll
                 for (int j2 = 0; j2 < 32; ++j2) {
                     const float2 o = v[slot32(j2)];
@@ -637,7 +667,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(TcParams p) 
                 TFNO_TRACE_SINCE(3);
                 fence_async_smem();
                 __syncwarp();
-                if (lane < G::OUT_ROWS) {
+                if (G::TENSOR_OUT && p.use_ymap) {
+                    if (lane == 0) {
+                        asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                                     ::"l"(reinterpret_cast<uint64_t>(&p.ymap)), "r"(0), "r"((int)row), "r"(t * GROUPS + qi * GPW),
+                                       "r"(smem_u32(ost)) : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else if (lane < G::OUT_ROWS) {
                     const int nn = t * GROUPS + qi * GPW + lane;
                     float2* dst = p.y + row * p.y_stride_row + (long long)nn * p.y_stride_n;
                     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
