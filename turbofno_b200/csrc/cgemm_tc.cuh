@@ -113,22 +113,45 @@ __global__ void __launch_bounds__(kGemmThreads, 1) cgemm_tc_kernel(CgemmTcParams
     // chunk c of a tile belongs to half-team h = c & 1; tph[h] = chunks of half-team h per tile
     const int tph0 = (NC + 1) / 2, tph1 = NC / 2;
 
-    // weights (times alpha) into tensor memory: thread i of warps 8-11 owns row i; rows 0-63
-    // produce Re, rows 64-127 Im of output channel n = i & 63
-    if (is_xfer) {
-        const int i = tid - 256, n = i & 63, im_row = i >> 6;
-        const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        for (int c = 0; c < NC; ++c) {
-            for (int part = 0; part < 2; ++part) {
-                for (int k0 = 0; k0 < CH; k0 += 8) {
+    // Weights (times alpha) into tensor memory; TMEM row i = 32 * (warp % 4) + lane; rows 0-63 produce
+    // Re, rows 64-127 Im of output channel n = i & 63.  A thread needs eight adjacent channels of its n,
+    // which in memory are 64 bytes every K*8 (or 8 bytes every N*8): read that way every warp-wide load
+    // touches 32 lines, and four warps doing 2K such loads each made the set-up of a launch ~10 us.  So
+    // all warps fetch the weights as contiguous runs with asynchronous 8-byte copies (one trip to memory)
+    // into the S buffers and planes, which nothing uses yet, as [n][K channels + 16 bytes], and warps
+    // 0-11 (three per TMEM quarter) convert from there.
+    {
+        static_assert(2 * 2 * (TN / 8) * s_sbo(4) + 2 * 64 * TN * 4 >= 64 * (64 * 8 + 16), "weight staging area (K <= 64)");
+        unsigned char* wst = sS;
+        const int wrow = K * 8 + 16;
+        const bool k_fast = p.w_stride_k == 1;
+#pragma unroll 1
+        for (int idx = tid; idx < 64 * K; idx += kGemmThreads) {
+            const int kk = k_fast ? idx % K : idx >> 6, nn = k_fast ? idx / K : idx & 63;
+            const float2* src = p.w + (long long)kk * p.w_stride_k + (long long)nn * p.w_stride_n;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(wst + nn * wrow + kk * 8)), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();
+        if (warp < 12) {
+            const int i = 32 * (warp & 3) + lane, n = i & 63, im_row = i >> 6;
+            const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+            for (int blk = warp >> 2; blk < K / 8; blk += 3) {      // eight channels c*CH + k0 .. +7
+                const int c = (8 * blk) / CH, k0 = (8 * blk) % CH;
+                float2 wv[8];
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const float4 t = *reinterpret_cast<const float4*>(wst + n * wrow + (8 * blk + j) * 8);
+                    wv[j] = cmul(make_float2(t.x, t.y), p.alpha);
+                    wv[j + 1] = cmul(make_float2(t.z, t.w), p.alpha);
+                }
+#pragma unroll
+                for (int part = 0; part < 2; ++part) {
                     uint32_t hi[8], lo[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const int k = c * CH + k0 + j;
-                        const float2 w0 = __ldg(p.w + (long long)k * p.w_stride_k + (long long)n * p.w_stride_n);
-                        const float2 wv = cmul(w0, p.alpha);
                         // Re row: [ Wr | -Wi ],  Im row: [ Wi | Wr ]  against  S = [ Ar ; Ai ]
-                        const float v = im_row ? (part ? wv.x : wv.y) : (part ? -wv.y : wv.x);
+                        const float v = im_row ? (part ? wv[j].x : wv[j].y) : (part ? -wv[j].y : wv[j].x);
                         const float h = tf32_hi(v);
                         hi[j] = __float_as_uint(h);
                         lo[j] = __float_as_uint(tf32_hi(v - h));
@@ -138,8 +161,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) cgemm_tc_kernel(CgemmTcParams
                     TFNO_TMEM_ST8(trow + TM_WLO + col, lo);
                 }
             }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();

@@ -103,7 +103,7 @@ struct TcParams {
 // SBO: bytes between 8-mode groups of the B operand S.  The contraction kernel of compact spectra
 // (cgemm_tc.cuh) stores 4-byte elements and uses s_sbo(4); the fused kernel stores the Re and Im
 // parts of a channel as one 8-byte element (column kk = 2*channel + part) and uses s_sbo_fused.
-__host__ __device__ inline int s_sbo(int R64) {
+__host__ __device__ constexpr int s_sbo(int R64) {
     const int span = (2 * (64 / R64) / 4) * kLBO;           // one chunk: CH channels, Re and Im rows
     return ((span + 63) / 64) * 64 + 16;
 }
@@ -112,11 +112,11 @@ __host__ __device__ inline int s_sbo(int R64) {
 //   R = 8: two channels give {0,8} bytes, lanes r, r+1 are ONE mode group apart   -> SBO = 16 mod 128
 //   R = 4: four channels give 32 bytes, lanes r, r+1 are TWO mode groups apart    -> 2*SBO = 32 mod 128
 // both hold for a span that is a multiple of 64, plus 16.
-__host__ __device__ inline int s_sbo_fused(int R) {
+__host__ __device__ constexpr int s_sbo_fused(int R) {
     const int span = (2 * (128 / R) / 4) * kLBO;
     return ((span + 63) / 64) * 64 + 16;
 }
-__host__ __device__ inline int s_bytes(int R) { return 8 * s_sbo_fused(R); }   // the hi or the lo array of one chunk buffer
+__host__ __device__ constexpr int s_bytes(int R) { return 8 * s_sbo_fused(R); }   // the hi or the lo array of one chunk buffer
 
 template <int R> struct Geometry {
     static constexpr int DY = 32 * R;
@@ -303,6 +303,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef TFNO_TC_TRACE
+    const long long tr_entry = clock64();
+    long long tr_dep = 0, tr_staged = 0, tr_conv = 0;
+#endif
     // Roles.  A scheduler partition hosts warps w, w+4, ...; giving it compute warps of the SAME role
     // keeps its instruction cache on one role's code.
     const bool is_compute = warp < kComputeWarps;
@@ -344,6 +348,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #endif
+#ifdef TFNO_TC_TRACE
+    tr_dep = clock64();
+#endif
     const long long first = blockIdx.x;
     const int n_it = first < p.rows ? (int)((p.rows - first + gridDim.x - 1) / gridDim.x) : 0;
     const long long n_loads = (long long)n_it * NC;
@@ -357,12 +364,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
     };
 
     // Weights into tensor memory.  Lane l of a warp with warp % 4 == q reaches TMEM row i = 32 q + l:
-    // rows 0-63 produce Re, rows 64-127 produce Im of output channel n = i & 63.  All 24 warps take
-    // part (six per quarter, each a sixth of the channels), so that the set-up of a short launch
-    // stays short.  Column kk of a chunk = 2 * channel + part: Re and Im of a channel are adjacent,
+    // rows 0-63 produce Re, rows 64-127 produce Im of output channel n = i & 63.  Twenty warps take
+    // part (five per quarter, each a fifth of the four-channel blocks), so that the set-up of a short
+    // launch stays short.  Column kk of a chunk = 2 * channel + part: Re and Im of a channel are adjacent,
     // matching the 8-byte stores of the forward warps.
-    // The producer warp first starts the copies of the first ring stages, so that the input rows
-    // travel while the weights are being converted.
     auto issue_load = [&](long long L) {       // whole producer warp; lanes < CH copy one row each
         const int s = stage_of((int)(L / NC), (int)(L % NC));
         const long long row = first + (L / NC) * gridDim.x;
@@ -374,50 +379,79 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
             bulk_load(smem_u32(ring + s * G::STAGE_BYTES + j * G::ROW_STRIDE), src, G::ROW_BYTES, bar(B_FULL + s));
         }
     };
+    // The producer warp starts the copies of the first ring stages and goes straight to its role
+    // (issuing them takes it ~5 k cycles); the other 23 warps bring the weights in meanwhile and
+    // meet at a named barrier of their own.
     long long preloaded = 0;
-    if (warp == kProducerWarp)
+    if (warp == kProducerWarp) {
         for (; preloaded < kStages && preloaded < n_loads; ++preloaded) issue_load(preloaded);
-    {
-        const int q = warp & 3, share = warp >> 2;                    // share 0..5 of quarter q
+    } else {
+        // Through shared memory: a thread needs (output n = its TMEM row, four adjacent channels),
+        // which in memory are 32 bytes every K*8 (or 8 bytes every N*8) -- read that way, every
+        // warp-wide load touches 32 lines and the set-up of a launch took 6 us.  Instead the warps
+        // fetch the weights as contiguous runs with asynchronous 8-byte copies, all in flight
+        // together (one trip to memory), into the S buffers and planes, which nothing uses yet, as
+        // [n][K channels + 16 bytes] (row stride = 16 mod 128 for K a multiple of 16: the 16-byte
+        // reads of a quarter-warp fall into distinct banks), and the 20 warps below the producer
+        // pick their values from there (five per TMEM quarter).
+        constexpr int kStagers = kTcThreads - 32, kConvShares = 5;
+        static_assert(kProducerWarp == 4 * kConvShares, "warps 0..19 convert");
+        static_assert(4 * s_bytes(R) + 2 * 64 * 256 + kInvWarps * G::OUT_BYTES >= 64 * (96 * 8 + 16), "weight staging area");
+        auto stagers_sync = [] { asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory"); };
+        unsigned char* wst = sS;
+        const int wrow = K * 8 + 16;
+        const bool k_fast = p.w_stride_k == 1;
+        const int stid = warp < kProducerWarp ? tid : tid - 32;
+        const int q = warp & 3, share = warp >> 2;                    // share 0..4 of quarter q (warps 0..19)
         const int i = 32 * q + lane, n = i & 63, im_row = i >> 6;
         const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16);
-        // all loads of a thread first (K <= 96: at most four blocks of four channels), then the
-        // conversion: one trip to memory instead of one per block
-        constexpr int kMaxBlocks = 4;
-        float2 wv[kMaxBlocks][4];
-#pragma unroll
-        for (int b = 0; b < kMaxBlocks; ++b) {
-            const int k0 = 4 * share + b * 4 * (kTcThreads / 128);
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                wv[b][j] = (k0 < K) ? __ldg(p.w + (long long)(k0 + j) * p.w_stride_k + (long long)n * p.w_stride_n) : make_float2(0.f, 0.f);
+#pragma unroll 1
+        for (int idx = stid; idx < 64 * K; idx += kStagers) {
+            const int kk = k_fast ? idx % K : idx >> 6, nn = k_fast ? idx / K : idx & 63;
+            const float2* src = p.w + (long long)kk * p.w_stride_k + (long long)nn * p.w_stride_n;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(wst + nn * wrow + kk * 8)), "l"(src) : "memory");
         }
-#pragma unroll
-        for (int b = 0; b < kMaxBlocks; ++b) {
-            const int k0 = 4 * share + b * 4 * (kTcThreads / 128);
-            if (k0 < K) {
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        stagers_sync();
+#ifdef TFNO_TC_TRACE
+        tr_staged = clock64();
+#endif
+        if (warp < kProducerWarp) {
+            for (int blk = share; blk < K / 4; blk += kConvShares) {
+                const float4 a = *reinterpret_cast<const float4*>(wst + n * wrow + blk * 32);
+                const float4 c = *reinterpret_cast<const float4*>(wst + n * wrow + blk * 32 + 16);
+                const float2 w4[4] = {make_float2(a.x, a.y), make_float2(a.z, a.w), make_float2(c.x, c.y), make_float2(c.z, c.w)};
                 uint32_t hi[8], lo[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int part = j & 1;
-                    const float2 w1 = wv[b][j >> 1];
+                    const float2 w1 = w4[j >> 1];
                     // Re row: [ Wr | -Wi ],  Im row: [ Wi | Wr ]  against  S = [ Xr ; Xi ]
                     const float v = im_row ? (part ? w1.x : w1.y) : (part ? -w1.y : w1.x);
                     const float h = tf32_hi(v);
                     hi[j] = __float_as_uint(h);
                     lo[j] = __float_as_uint(tf32_hi(v - h));
                 }
-                TFNO_TMEM_ST8(trow + TM_WHI + 2 * k0, hi);
-                TFNO_TMEM_ST8(trow + TM_WLO + 2 * k0, lo);
+                TFNO_TMEM_ST8(trow + TM_WHI + 8 * blk, hi);
+                TFNO_TMEM_ST8(trow + TM_WLO + 8 * blk, lo);
             }
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        if (warp < kProducerWarp) asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+#ifdef TFNO_TC_TRACE
+        tr_conv = clock64();
+#endif
+        // the MMA thread may read the weights, and the planes area is free, once all of them are here
+        tc_fence_before();
+        stagers_sync();
+        tc_fence_after();
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
 
     TFNO_TRACE_DECL
+#ifdef TFNO_TC_TRACE
+    // helpers: from kernel entry until the dependency wait returned (out) / the first pass of the weights is
+    // in shared memory (in) / the weights are in tensor memory (mid) / the roles start (loop)
+    if (!is_compute) { tr_wait[9] = tr_dep - tr_entry; tr_wait[7] = tr_staged - tr_entry; tr_wait[8] = tr_conv - tr_entry; tr_wait[10] = tr_t0 - tr_entry; }
+#endif
     if (!is_compute) {
         // ============ warpgroups 4 and 5: accumulator hand-off, data movement, MMA issue ============
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kHelperRegs) : "memory");
