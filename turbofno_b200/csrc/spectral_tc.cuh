@@ -41,6 +41,7 @@
 // returns.
 #pragma once
 #include <cstdint>
+#include <type_traits>
 #include <cuda.h>          // CUtensorMap (types only: the encoder is fetched from the runtime)
 #include "fft32.cuh"
 
@@ -284,7 +285,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int K = p.K;
-    const int NC = K / CH;                            // chunks per row
+    const int NC = K / CH;                            // chunks per row (a compile-time NC measured 4 % slower)
     const int SBO = s_sbo_fused(R), SBYTES = s_bytes(R);
     unsigned char* ring = base;
     unsigned char* sS = ring + kStages * G::STAGE_BYTES;            // [buffer 0: hi | lo][buffer 1: hi | lo]
@@ -296,7 +297,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
     // barrier indices
     constexpr int B_FULL = 0, B_EMPTY = kStages, B_SFULL = 2 * kStages, B_SEMPTY = B_SFULL + 2, B_AFULL = B_SEMPTY + 2,
                   B_AEMPTY = B_AFULL + 2, B_PFULL = B_AEMPTY + 2, B_PEMPTY = B_PFULL + 1, B_STAGGER = B_PEMPTY + 1,
-                  B_DRAIN = B_STAGGER + 2, B_COUNT = B_DRAIN + 1;
+                  B_DRAIN = B_STAGGER + 2, B_HELP = B_DRAIN + 1, B_COUNT = B_HELP + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
@@ -325,6 +326,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
         mbar_init(bar(B_STAGGER), 4);
         mbar_init(bar(B_STAGGER + 1), 4);
         mbar_init(bar(B_DRAIN), 1);
+        mbar_init(bar(B_HELP), 4);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -480,7 +482,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) { mbar_arrive(bar(B_AEMPTY + buf)); mbar_arrive(bar(B_PFULL)); }
+                if (lane == 0) {
+                    mbar_arrive(bar(B_AEMPTY + buf));
+                    mbar_arrive(bar(B_PFULL));
+                    if (it == n_it - 1) mbar_arrive(bar(B_HELP));      // the forward warps help with the last row
+                }
             }
         } else if (warp == kProducerWarp) {
             // producer: keeps the ring full
@@ -544,20 +550,43 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
     const int kl = wl * GPW + g;                      // forward: channel inside the chunk
     const int qi = warp >> 1;                         // inverse: 0..7
     constexpr int GROUPS = kInvWarps * GPW;           // inverse: channels per pass
-    const int tasks_per_row = is_fwd ? (NC - half + 1) / 2 : 64 / GROUPS;
-    const float2 coef = is_fwd ? round1_coef32<R>(r) : inverse_fold_coef32<R>(r, INVERSE);   // forward: round 1; inverse: W_R^{-+r}
+    const int fwd_tasks = (NC - half + 1) / 2;
+    constexpr int kInvTasks = 64 / GROUPS;
+    // Drain: while the inverse warps finish the last row of the CTA the forward warps would idle, so
+    // they turn into inverse warps and take the second half of that row's tasks (phase 1 below).
+    // They stage their output rows in the ring: warp qi = 4*half + wl gets the bytes of ITS rows of
+    // ITS half-team's stage (OUT_BYTES = GPW * ROW_STRIDE), which it has read for the last time and
+    // which no copy targets any more.  Needs staged output (DY >= 256: two or more tasks per row)
+    // and a stage per half-team (two or more chunks per row).
+#ifndef TFNO_NO_DRAIN_HELP
+    const bool drain_help = G::STAGED_OUT && kInvTasks >= 2 && NC >= 2 && n_it > 0;
+#else
+    const bool drain_help = false;
+#endif
+    static_assert(!G::STAGED_OUT || kStages * G::STAGE_BYTES == kInvWarps * G::OUT_BYTES, "the ring holds one staging buffer per helping warp");
     bool alive = true;
 
     TFNO_TRACE_MARK();
-    for (int it = 0; it < n_it && alive; ++it) {
+    // The task loops exist twice in the binary: the main copy (phase 0, both roles) and the copy the
+    // forward warps run once, as inverse warps, on the last row (phase 1).  Two instantiations rather
+    // than a run-time phase: the extra live state of a shared copy cost the main loop 10 %.
+    auto run_tasks = [&](auto phase_tag) {
+    constexpr int phase = decltype(phase_tag)::value;
+    const bool fwd = phase ? false : is_fwd;          // the role this warp plays in this phase
+    const float2 coef = fwd ? round1_coef32<R>(r) : inverse_fold_coef32<R>(r, INVERSE);   // forward: round 1; inverse: W_R^{-+r}
+    for (int it = phase ? n_it - 1 : 0; it < n_it && alive; ++it) {
         const long long row = first + (long long)it * gridDim.x;
-        for (int t = 0; t < tasks_per_row && alive; ++t) {
+        int t_lo = 0, t_hi = fwd ? fwd_tasks : kInvTasks;
+        if (!fwd && drain_help && it == n_it - 1) {
+            if (phase) t_lo = kInvTasks / 2; else t_hi = kInvTasks / 2;
+        }
+        for (int t = t_lo; t < t_hi && alive; ++t) {
             TFNO_TRACE_SINCE(10);
             float2 v[32];
             float sgn = 1.0f;
             int n = 0, s = 0;
             // ------------------------------ prologue ------------------------------
-            if (is_fwd) {
+            if (fwd) {
                 const int c = half + 2 * t;
                 s = stage_of(it, c);
                 const uint32_t u = use_of(it, c);
@@ -575,7 +604,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
                 TFNO_TRACE_SINCE(7);
                 sgn = lane_rotated32<R>(r) ? -1.0f : 1.0f;
             } else {
-                if (t == 0) {
+                if (t == 0 && phase == 0) {
                     alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(0, mbar_wait(bar(B_PFULL), it & 1, abort_flag, p.status, 43)));
                     if (!alive) break;
                 }
@@ -601,7 +630,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
                     v[4 * cc + 2] = INVERSE ? make_float2(u2.y, u2.x) : u2;
                     v[4 * cc + 3] = INVERSE ? make_float2(u3.y, u3.x) : u3;
                 }
-                if (t == tasks_per_row - 1) {
+                if (phase == 0 && t == t_hi - 1) {
                     // the planes have been read for the last time this row; the fence orders the
                     // loads above before the release (their values are consumed only later)
                     __threadfence_block();
@@ -614,19 +643,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
             // ------------------------------ the one 32-point transform ------------------------------
             if (stagger_pending && (warp >> 3) == 1) {
                 // once: the second half waits until its partition mates have finished a first transform
-                alive = __all_sync(0xffffffffu, mbar_wait(bar(B_STAGGER + (is_fwd ? 0 : 1)), 0, abort_flag, p.status, 51));
+                alive = __all_sync(0xffffffffu, mbar_wait(bar(B_STAGGER + (fwd ? 0 : 1)), 0, abort_flag, p.status, 51));
                 if (!alive) break;
             }
             fft32<-1>(v, sgn);
             TFNO_TRACE_SINCE(6);
             if (stagger_pending && (warp >> 3) == 0) {
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_STAGGER + (is_fwd ? 0 : 1)));
+                if (lane == 0) mbar_arrive(bar(B_STAGGER + (fwd ? 0 : 1)));
             }
             stagger_pending = false;
 
             // ------------------------------ epilogue ------------------------------
-            if (is_fwd) {
+            if (fwd) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
                     const float4 tt = *reinterpret_cast<const float4*>(twF + tw_index<R>(r, j));
@@ -642,7 +671,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
                 // lane r now holds modes 64/R*r + j, j < 64/R, in v[slot32(j)]
                 TFNO_TRACE_SINCE(8);
                 // this half-team's S buffer is free once the MMAs of its previous chunk have completed
-                const uint32_t jchunk = (uint32_t)it * (uint32_t)tasks_per_row + (uint32_t)t;
+                const uint32_t jchunk = (uint32_t)it * (uint32_t)fwd_tasks + (uint32_t)t;
                 alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(1, mbar_wait(bar(B_SEMPTY + half), (jchunk & 1) ^ 1, abort_flag, p.status, 32)));
                 if (!alive) break;
                 constexpr int PER = 64 / R;
@@ -686,7 +715,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
                 // bulk-copy engine: the rows leave as full lines instead of 32-byte pieces through
                 // the load/store unit.  The lanes that issue the copies first wait until their
                 // previous copies have finished reading the staging buffer.
-                unsigned char* ost = ostage + qi * G::OUT_BYTES;
+                unsigned char* ost = (phase ? ring : ostage) + qi * G::OUT_BYTES;
                 if (lane < G::OUT_ROWS) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 __syncwarp();
                 TFNO_TRACE_SINCE(2);
@@ -720,7 +749,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
             }
         }
     }
-    if (is_inv) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all output rows have landed
+    };   // run_tasks
+    run_tasks(std::integral_constant<int, 0>{});
+    if (is_fwd && drain_help && alive) {
+        stagger_pending = false;
+        // the planes hold the last row (a barrier of its own: the forward warps have not followed
+        // the phases of B_PFULL, and a parity wait cannot tell "not yet" from "two phases on")
+        alive = __all_sync(0xffffffffu, mbar_wait(bar(B_HELP), 0, abort_flag, p.status, 44));
+        if (alive) run_tasks(std::integral_constant<int, 1>{});
+    }
+    if (is_inv || drain_help) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all output rows have landed
     }   // forward / inverse warps
 
     // ---------------- teardown ----------------
