@@ -553,7 +553,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
     const int fwd_tasks = (NC - half + 1) / 2;
     constexpr int kInvTasks = 64 / GROUPS;
     // Drain: while the inverse warps finish the last row of the CTA the forward warps would idle, so
-    // they turn into inverse warps and take the second half of that row's tasks (phase 1 below).
+    // they turn into inverse warps and take the upper half of that row's tasks (phase 1 below).
     // They stage their output rows in the ring: warp qi = 4*half + wl gets the bytes of ITS rows of
     // ITS half-team's stage (OUT_BYTES = GPW * ROW_STRIDE), which it has read for the last time and
     // which no copy targets any more.  Needs staged output (DY >= 256: two or more tasks per row)
@@ -567,19 +567,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
     bool alive = true;
 
     TFNO_TRACE_MARK();
-    // The task loops exist twice in the binary: the main copy (phase 0, both roles) and the copy the
-    // forward warps run once, as inverse warps, on the last row (phase 1).  Two instantiations rather
-    // than a run-time phase: the extra live state of a shared copy cost the main loop 10 %.
+    // The task loops exist twice in the binary: the main copy (phase 0, both roles) and a copy that
+    // runs the inverse tasks of the CTA's last row on all sixteen compute warps (phase 1).  Two
+    // instantiations rather than a run-time phase: the extra live state of a shared copy cost the
+    // main loop 10 %.
     auto run_tasks = [&](auto phase_tag) {
     constexpr int phase = decltype(phase_tag)::value;
     const bool fwd = phase ? false : is_fwd;          // the role this warp plays in this phase
     const float2 coef = fwd ? round1_coef32<R>(r) : inverse_fold_coef32<R>(r, INVERSE);   // forward: round 1; inverse: W_R^{-+r}
-    for (int it = phase ? n_it - 1 : 0; it < n_it && alive; ++it) {
+    // phase 0: all rows (inverse warps: all but the last when the forward warps help); phase 1: the
+    // last row's inverse tasks, lower half on the inverse warps, upper half on the forward warps
+    const int it_end = (phase == 0 && !fwd && drain_help) ? n_it - 1 : n_it;
+    const int t_lo = phase ? (is_fwd ? kInvTasks / 2 : 0) : 0;
+    const int t_hi = phase ? (is_fwd ? kInvTasks : kInvTasks / 2) : (fwd ? fwd_tasks : kInvTasks);
+    const bool wait_planes = phase == 0 || !is_fwd;
+    for (int it = phase ? n_it - 1 : 0; it < it_end && alive; ++it) {
         const long long row = first + (long long)it * gridDim.x;
-        int t_lo = 0, t_hi = fwd ? fwd_tasks : kInvTasks;
-        if (!fwd && drain_help && it == n_it - 1) {
-            if (phase) t_lo = kInvTasks / 2; else t_hi = kInvTasks / 2;
-        }
         for (int t = t_lo; t < t_hi && alive; ++t) {
             TFNO_TRACE_SINCE(10);
             float2 v[32];
@@ -604,7 +607,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
                 TFNO_TRACE_SINCE(7);
                 sgn = lane_rotated32<R>(r) ? -1.0f : 1.0f;
             } else {
-                if (t == 0 && phase == 0) {
+                if (t == t_lo && wait_planes) {
                     alive = __all_sync(0xffffffffu, TFNO_TRACE_STEP(0, mbar_wait(bar(B_PFULL), it & 1, abort_flag, p.status, 43)));
                     if (!alive) break;
                 }
@@ -715,7 +718,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
                 // bulk-copy engine: the rows leave as full lines instead of 32-byte pieces through
                 // the load/store unit.  The lanes that issue the copies first wait until their
                 // previous copies have finished reading the staging buffer.
-                unsigned char* ost = (phase ? ring : ostage) + qi * G::OUT_BYTES;
+                unsigned char* ost = ((phase && is_fwd) ? ring : ostage) + qi * G::OUT_BYTES;
                 if (lane < G::OUT_ROWS) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 __syncwarp();
                 TFNO_TRACE_SINCE(2);
@@ -751,11 +754,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
     }
     };   // run_tasks
     run_tasks(std::integral_constant<int, 0>{});
-    if (is_fwd && drain_help && alive) {
+    if (drain_help && alive) {
         stagger_pending = false;
-        // the planes hold the last row (a barrier of its own: the forward warps have not followed
-        // the phases of B_PFULL, and a parity wait cannot tell "not yet" from "two phases on")
-        alive = __all_sync(0xffffffffu, mbar_wait(bar(B_HELP), 0, abort_flag, p.status, 44));
+        // The forward warps wait for the planes of the last row on a barrier of their own: they have
+        // not followed the phases of B_PFULL, and a parity wait cannot tell "not yet" from "two
+        // phases on".  The inverse warps wait on B_PFULL as in every row.
+        if (is_fwd) alive = __all_sync(0xffffffffu, mbar_wait(bar(B_HELP), 0, abort_flag, p.status, 44));
         if (alive) run_tasks(std::integral_constant<int, 1>{});
     }
     if (is_inv || drain_help) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all output rows have landed
