@@ -195,6 +195,32 @@ inline bool encode_output_map(CUtensorMap* map, float2* y, int len, long long ro
                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Encoding a map costs the host several microseconds, which a launch of ~70 us that is issued
+// back to back (eight ranks on one host) does not hide: keep the last maps, keyed by everything
+// that goes into one.  A map holds an address and a geometry, nothing that can go stale.
+inline bool cached_output_map(CUtensorMap* map, int device, float2* y, int len, long long rows, int channels,
+                              long long stride_row, long long stride_n, int box_channels) {
+    struct Entry { bool valid; int device, len, channels, box; const void* y; long long rows, sr, sn; CUtensorMap map; };
+    constexpr int kEntries = 32;
+    static std::mutex mu;
+    static Entry table[kEntries] = {};
+    static unsigned next = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Entry& e : table)
+        if (e.valid && e.device == device && e.y == y && e.len == len && e.rows == rows && e.channels == channels &&
+            e.sr == stride_row && e.sn == stride_n && e.box == box_channels) {
+            *map = e.map;
+            return true;
+        }
+    CUtensorMap m;
+    if (!encode_output_map(&m, y, len, rows, channels, stride_row, stride_n, box_channels)) return false;
+    Entry& e = table[next++ % kEntries];
+    e.valid = true; e.device = device; e.len = len; e.channels = channels; e.box = box_channels; e.y = y;
+    e.rows = rows; e.sr = stride_row; e.sn = stride_n; e.map = m;
+    *map = m;
+    return true;
+}
+
 template <int R, bool INVERSE>
 inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
     auto kernel = tc::spectral_tc_kernel<R, INVERSE>;
@@ -224,7 +250,7 @@ inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream
     q.inv_gain = p.inv_gain; q.conj_inverse = p.conj_inverse; q.status = dev.status;
 #ifndef TFNO_NO_TENSOR_STORE
     if constexpr (tc::Geometry<R>::TENSOR_OUT)
-        q.use_ymap = encode_output_map(&q.ymap, p.y, 32 * R, p.rows, 64, p.y_stride_row, p.y_stride_n, tc::Geometry<R>::GPW) ? 1 : 0;
+        q.use_ymap = cached_output_map(&q.ymap, dev.device, p.y, 32 * R, p.rows, 64, p.y_stride_row, p.y_stride_n, tc::Geometry<R>::GPW) ? 1 : 0;
 #endif
     long long grid = dev.sms;
     if (grid > p.rows) grid = p.rows;
