@@ -93,7 +93,9 @@ def test_plan_reports_the_kernels_it_launches(cuda):
     # everything else: the FP32 row-tile kernel
     assert kernels(1, 1, 128, 8, 64) == ["spectral_tile_kernel<2,1,1,1>"]
     assert kernels(1, 5, 256, 32, 128) == ["spectral_tile_kernel<4,1,1,2>"]
-    assert kernels(1, 300, 256, 128, 64) == ["spectral_tile_kernel<4,1,1,1>"]
+    assert kernels(1, 300, 256, 128, 64) == ["spectral_tc_kernel<8,1>", "spectral_tc_kernel<8,1>+="]    # 64 + 64 channels
+    assert kernels(1, 100, 256, 128, 64) == ["spectral_tile_kernel<4,1,1,1>"]                          # too few rows for two launches
+    assert kernels(1, 300, 256, 200, 64) == ["spectral_tile_kernel<4,1,1,1>"]                          # more than two parts
     assert kernels(1, 3, 512, 128, 64) == ["spectral_tile_kernel<8,1,1,1>"]
     # long transforms run the fused tensor-core kernel too (chunks of 8 and 4 channels)
     assert kernels(1, 3, 512, 16, 64) == ["spectral_tc_kernel<16,1>"]

@@ -127,6 +127,28 @@ def test_fused_kernel_chunk_counts_many_rows_per_sm(cuda, DY, K):
     assert_close(run_1d(cuda, x, w, "D"), oracle_c.spectral_conv_1d(x, w), "fused, %d channels at DY=%d" % (K, DY))
 
 
+@pytest.mark.parametrize("DY,K,N", [(256, 128, 64), (256, 112, 64), (128, 128, 64), (128, 192, 64), (512, 104, 64), (1024, 104, 64),
+                                    (256, 128, 128)])
+def test_more_than_96_channels_run_the_fused_kernel_in_two_accumulating_launches(cuda, DY, K, N):
+    """The weights of at most 96 channels fit tensor memory; up to 192 channels are split into two
+    launches, the second adding to the first's output through the copy engine (or, at DY=128, in
+    registers).  The output buffer is pre-filled with NaN: the first launch must overwrite it."""
+    import torch
+    import turbofno_b200 as t
+
+    B = 449
+    plan = t.SpectralConv(1, B, DY, K, N, variant="D")
+    name = "spectral_tc_kernel<%d,1>" % (DY // 32)
+    assert plan.kernels() == [name, name + "+="] * (N // 64)
+    x, w = oracle_np.make_inputs_1d(B, K, N, DY, seed=DY + K)
+    xt = torch.from_numpy(np.ascontiguousarray(np.swapaxes(x, 0, 1))).to(cuda)
+    wt = torch.from_numpy(np.ascontiguousarray(w.T)).to(cuda)
+    y = torch.full((N, B, DY), float("nan"), dtype=torch.complex64, device=cuda)
+    plan(xt, wt, y=y)
+    plan.close()
+    assert_close(np.swapaxes(y.cpu().numpy(), 0, 1), oracle_c.spectral_conv_1d(x, w), "%d channels at DY=%d" % (K, DY))
+
+
 def test_wide_layer_runs_the_fused_kernel_per_block_of_64_outputs(cuda):
     # N = 128 and 192 with enough rows for the tensor-core kernel (two rows per SM and more)
     for (B, K, N, DY) in [(300, 32, 128, 256), (300, 64, 192, 128)]:

@@ -152,13 +152,24 @@ inline int launch_tile_r(const DeviceInfo& dev, int R, const TileParams& p, cuda
 // Tensor-core fused kernel: N a multiple of 64 (64 per launch), K a multiple of the chunk size
 // (4096 / DY channels: 32, 16, 8, 4 at DY = 128, 256, 512, 1024) up to 96 (tensor memory holds the
 // weights, 4K columns, next to two accumulators), transform length 128 to 1024.
+// Channels per launch of the fused tensor-core kernel: the weights of at most 96 channels fit tensor
+// memory, so more channels (up to 192, a multiple of the chunk size) are split into two launches,
+// the second adding its result to the first's (both halves multiples of the chunk size).
+inline int tc_first_part(int K, int CH) {
+    if (K <= 96) return K;
+    const int half = ((K / 2 + CH - 1) / CH) * CH;
+    return half;
+}
 inline bool tc_eligible(const DeviceInfo& dev, int len, const TileParams& p) {
     if (!dev.use_tensor_cores || !dev.status) return false;
     if (p.N % 64 != 0 || !supported_len(len)) return false;
-    // N > 64 takes one launch per 64 output channels: worth it only when the launches are long
-    if (p.N > 64 && p.rows < 2LL * dev.sms) return false;
     const int CH = 128 / (len / 32);
-    return p.K >= CH && p.K <= 96 && p.K % CH == 0;
+    if (p.K < CH || p.K > 192 || p.K % CH != 0) return false;
+    const int launches = (p.N / 64) * (p.K > 96 ? 2 : 1);
+    // several launches (one per 64 output channels and per part of the channels, each re-reading
+    // its input): worth it only when the launches are long
+    if (launches > 1 && p.rows < 2LL * dev.sms) return false;
+    return tc_first_part(p.K, CH) <= 96 && p.K - tc_first_part(p.K, CH) <= 96;
 }
 
 // cuTensorMapEncodeTiled of the installed driver, looked up through the runtime (the library does
@@ -222,11 +233,11 @@ inline bool cached_output_map(CUtensorMap* map, int device, float2* y, int len, 
 }
 
 template <int R, bool INVERSE>
-inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
+inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st, bool accumulate = false) {
     auto kernel = tc::spectral_tc_kernel<R, INVERSE>;
     const size_t smem = tc::tc_smem_bytes<R>(p.K);
     if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
-    if (record_launch(dev, "spectral_tc_kernel<%d,%d>", R, INVERSE)) return TFNO_OK;
+    if (record_launch(dev, accumulate ? "spectral_tc_kernel<%d,%d>+=" : "spectral_tc_kernel<%d,%d>", R, INVERSE)) return TFNO_OK;
     int occ = 0;
     int rc = prepare_kernel(kernel, smem, dev, &occ, tc::kTcThreads);
     if (rc != TFNO_OK) return rc;
@@ -248,9 +259,10 @@ inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream
     q.w = p.w; q.w_stride_k = p.w_stride_k; q.w_stride_n = p.w_stride_n;
     q.y = p.y; q.y_stride_row = p.y_stride_row; q.y_stride_n = p.y_stride_n;
     q.inv_gain = p.inv_gain; q.conj_inverse = p.conj_inverse; q.status = dev.status;
+    q.accumulate = accumulate ? 1 : 0;
 #ifndef TFNO_NO_TENSOR_STORE
     if constexpr (tc::Geometry<R>::TENSOR_OUT)
-        q.use_ymap = cached_output_map(&q.ymap, dev.device, p.y, 32 * R, p.rows, 64, p.y_stride_row, p.y_stride_n, tc::Geometry<R>::GPW) ? 1 : 0;
+        if (!accumulate) q.use_ymap = cached_output_map(&q.ymap, dev.device, p.y, 32 * R, p.rows, 64, p.y_stride_row, p.y_stride_n, tc::Geometry<R>::GPW) ? 1 : 0;
 #endif
     long long grid = dev.sms;
     if (grid > p.rows) grid = p.rows;
@@ -332,19 +344,25 @@ inline int launch_tile(const DeviceInfo& dev, int len, TileParams p, cudaStream_
             // The tensor-core kernel produces 64 output channels (its 128 accumulator rows); wider
             // layers run it once per block of 64, re-reading the input (still faster than the FP32
             // kernel: 1.0 against 1.7 ms at bs=8192, K=64, N=128, DY=256).
+            const int K1 = tc_first_part(p.K, 128 / (len / 32));
             for (int n0 = 0; n0 < p.N; n0 += 64) {
-                TileParams q = p;
-                q.N = 64;
-                q.w = p.w + (long long)n0 * p.w_stride_n;
-                q.y = p.y + (long long)n0 * p.y_stride_n;
-                int rc = TFNO_ERR_UNSUPPORTED;
-                switch (len / 32) {            // lanes per signal
-                    case 4: rc = q.conj_inverse ? launch_tc_inst<4, true>(dev, q, st) : launch_tc_inst<4, false>(dev, q, st); break;
-                    case 8: rc = q.conj_inverse ? launch_tc_inst<8, true>(dev, q, st) : launch_tc_inst<8, false>(dev, q, st); break;
-                    case 16: rc = q.conj_inverse ? launch_tc_inst<16, true>(dev, q, st) : launch_tc_inst<16, false>(dev, q, st); break;
-                    case 32: rc = q.conj_inverse ? launch_tc_inst<32, true>(dev, q, st) : launch_tc_inst<32, false>(dev, q, st); break;
+                for (int k0 = 0; k0 < p.K; k0 += K1) {         // one or two parts of the channels
+                    TileParams q = p;
+                    q.N = 64;
+                    q.K = (k0 == 0) ? K1 : p.K - K1;
+                    q.x = p.x + (long long)k0 * p.x_stride_k;
+                    q.w = p.w + (long long)n0 * p.w_stride_n + (long long)k0 * p.w_stride_k;
+                    q.y = p.y + (long long)n0 * p.y_stride_n;
+                    const bool acc = k0 != 0;
+                    int rc = TFNO_ERR_UNSUPPORTED;
+                    switch (len / 32) {            // lanes per signal
+                        case 4: rc = q.conj_inverse ? launch_tc_inst<4, true>(dev, q, st, acc) : launch_tc_inst<4, false>(dev, q, st, acc); break;
+                        case 8: rc = q.conj_inverse ? launch_tc_inst<8, true>(dev, q, st, acc) : launch_tc_inst<8, false>(dev, q, st, acc); break;
+                        case 16: rc = q.conj_inverse ? launch_tc_inst<16, true>(dev, q, st, acc) : launch_tc_inst<16, false>(dev, q, st, acc); break;
+                        case 32: rc = q.conj_inverse ? launch_tc_inst<32, true>(dev, q, st, acc) : launch_tc_inst<32, false>(dev, q, st, acc); break;
+                    }
+                    if (rc != TFNO_OK) return rc;
                 }
-                if (rc != TFNO_OK) return rc;
             }
             return TFNO_OK;
         }

@@ -98,6 +98,11 @@ struct TcParams {
     // instruction instead of one per row (each costs the issuing warp ~175 cycles).  DY = 256 only
     // (a box is at most 256 elements wide); 0 = not available, the rows leave one by one.
     int use_ymap;
+    // 1: y += result instead of y = result (the copy engine adds: cp.reduce.async.bulk .add.f32).  This
+    // is how K > 96 runs: the channels are split into two launches, the second accumulating.  The
+    // tiled copy is not used then (its map has 8-byte elements; a float map's box could hold only
+    // half a row).
+    int accumulate;
     alignas(64) CUtensorMap ymap;
 };
 
@@ -710,8 +715,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
                         float2 got;
                         got.x = __shfl_xor_sync(0xffffffffu, send.x, 1);
                         got.y = __shfl_xor_sync(0xffffffffu, send.y, 1);
-                        *reinterpret_cast<float4*>(dst + 2 * R * n2) =
-                            odd ? make_float4(got.x, got.y, od.x, od.y) : make_float4(ev.x, ev.y, got.x, got.y);
+                        float4 o4 = odd ? make_float4(got.x, got.y, od.x, od.y) : make_float4(ev.x, ev.y, got.x, got.y);
+                        if (p.accumulate) {
+                            const float4 prev = *reinterpret_cast<const float4*>(dst + 2 * R * n2);
+                            o4.x += prev.x; o4.y += prev.y; o4.z += prev.z; o4.w += prev.w;
+                        }
+                        *reinterpret_cast<float4*>(dst + 2 * R * n2) = o4;
                     }
                 } else {
                 // Stage the warp's OUT_ROWS output rows in shared memory and hand each row to the
@@ -743,8 +752,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
                 } else if (lane < G::OUT_ROWS) {
                     const int nn = t * GROUPS + qi * GPW + lane;
                     float2* dst = p.y + row * p.y_stride_row + (long long)nn * p.y_stride_n;
-                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-                                 ::"l"(dst), "r"(smem_u32(ost + lane * G::OUT_STRIDE)), "r"(G::ROW_BYTES) : "memory");
+                    if (p.accumulate)
+                        asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+                                     ::"l"(dst), "r"(smem_u32(ost + lane * G::OUT_STRIDE)), "r"(G::ROW_BYTES) : "memory");
+                    else
+                        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                     ::"l"(dst), "r"(smem_u32(ost + lane * G::OUT_STRIDE)), "r"(G::ROW_BYTES) : "memory");
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
                 }
