@@ -112,11 +112,13 @@ def test_wide_channels(cuda):
 
 
 @pytest.mark.parametrize("DY,K", [(256, 16), (256, 32), (256, 48), (256, 64), (256, 96), (128, 32), (128, 64), (128, 96),
-                                  (512, 8), (512, 40), (512, 64), (1024, 24), (1024, 64)])
+                                  (512, 8), (512, 40), (512, 64), (1024, 24), (1024, 64),
+                                  # a last chunk with fewer channels than the chunk size (16 at DY=256, 32 at DY=128)
+                                  (256, 8), (256, 24), (256, 40), (256, 88), (128, 8), (128, 24), (128, 56), (128, 88)])
 def test_fused_kernel_chunk_counts_many_rows_per_sm(cuda, DY, K):
-    """One to sixteen chunks of channels per row, even and odd counts, at every transform length of
-    the fused tensor-core kernel, with three to four rows per SM so that every ring stage, S buffer
-    and accumulator buffer is reused."""
+    """One to sixteen chunks of channels per row, even and odd counts, full and partial last chunks,
+    at every transform length of the fused tensor-core kernel, with three to four rows per SM so
+    that every ring stage, S buffer and accumulator buffer is reused."""
     import turbofno_b200 as t
 
     probe = t.SpectralConv(1, 449, DY, K, 64, variant="D")
@@ -128,7 +130,7 @@ def test_fused_kernel_chunk_counts_many_rows_per_sm(cuda, DY, K):
 
 
 @pytest.mark.parametrize("DY,K,N", [(256, 128, 64), (256, 112, 64), (128, 128, 64), (128, 192, 64), (512, 104, 64), (1024, 104, 64),
-                                    (256, 128, 128)])
+                                    (256, 128, 128), (256, 104, 64), (256, 120, 64), (128, 104, 64), (128, 136, 64)])
 def test_more_than_96_channels_run_the_fused_kernel_in_two_accumulating_launches(cuda, DY, K, N):
     """The weights of at most 96 channels fit tensor memory; up to 192 channels are split into two
     launches, the second adding to the first's output through the copy engine (or, at DY=128, in

@@ -156,7 +156,7 @@ inline int launch_tile_r(const DeviceInfo& dev, int R, const TileParams& p, cuda
 // memory, so more channels (up to 192, a multiple of the chunk size) are split into two launches,
 // the second adding its result to the first's (both halves multiples of the chunk size).
 inline int tc_first_part(int K, int CH) {
-    if (K <= 96) return K;
+    if (((K + CH - 1) / CH) * CH <= 96) return K;
     const int half = ((K / 2 + CH - 1) / CH) * CH;
     return half;
 }
@@ -164,12 +164,17 @@ inline bool tc_eligible(const DeviceInfo& dev, int len, const TileParams& p) {
     if (!dev.use_tensor_cores || !dev.status) return false;
     if (p.N % 64 != 0 || !supported_len(len)) return false;
     const int CH = 128 / (len / 32);
-    if (p.K < CH || p.K > 192 || p.K % CH != 0) return false;
-    const int launches = (p.N / 64) * (p.K > 96 ? 2 : 1);
+    // K a multiple of 8; a last chunk of fewer than CH channels is padded with zero weights
+    if (p.K < 8 || p.K > 192 || p.K % 8 != 0) return false;
+    const int K1 = tc_first_part(p.K, CH), K2 = p.K - K1;
+    if (K1 > 96 || ((K2 + CH - 1) / CH) * CH > 96) return false;
+    const int launches = (p.N / 64) * (K2 ? 2 : 1);
     // several launches (one per 64 output channels and per part of the channels, each re-reading
     // its input): worth it only when the launches are long
     if (launches > 1 && p.rows < 2LL * dev.sms) return false;
-    return tc_first_part(p.K, CH) <= 96 && p.K - tc_first_part(p.K, CH) <= 96;
+    // a padded last chunk is wasted work: below one row per SM the FP32 kernel is as fast
+    if (p.K % CH != 0 && p.rows < dev.sms) return false;
+    return true;
 }
 
 // cuTensorMapEncodeTiled of the installed driver, looked up through the runtime (the library does

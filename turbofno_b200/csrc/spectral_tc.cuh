@@ -289,8 +289,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
     constexpr int CH = G::CH, GPW = G::GPW;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int K = p.K;
-    const int NC = K / CH;                            // chunks per row (a compile-time NC measured 4 % slower)
+    const int K = p.K;                                // a multiple of 4
+    const int NC = (K + CH - 1) / CH;                 // chunks per row (a compile-time NC measured 4 % slower)
+    // A last chunk with fewer than CH channels: the copies bring only its channels, the weights of
+    // the missing ones are zero in tensor memory, and the rows of the ring that no copy ever writes
+    // are zeroed once below -- the forward warps transform whatever the other rows hold (finite
+    // values of earlier chunks) and the zero weights remove it.  The task loops do not change.
+    const int Kp = NC * CH;
     const int SBO = s_sbo_fused(R), SBYTES = s_bytes(R);
     unsigned char* ring = base;
     unsigned char* sS = ring + kStages * G::STAGE_BYTES;            // [buffer 0: hi | lo][buffer 1: hi | lo]
@@ -339,13 +344,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (Kp != K) {
+        for (int i = tid; i < kStages * G::STAGE_BYTES / 16; i += kTcThreads) reinterpret_cast<uint4*>(ring)[i] = make_uint4(0u, 0u, 0u, 0u);
+        fence_async_smem();                            // before the copy engine writes other rows of the same stages
+    }
     fill_forward_table32<R>(twF, tid, kTcThreads);
     fill_inverse_table32_folded<R>(twI, tid, kTcThreads, p.inv_gain, INVERSE);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t TM_WHI = 0, TM_WLO = 2 * K, TM_ACC = 4 * K;        // column offsets; accumulators 2 x 64 columns
+    const uint32_t TM_WHI = 0, TM_WLO = 2 * Kp, TM_ACC = 4 * Kp;      // column offsets; accumulators 2 x 64 columns
 
 #ifndef TFNO_NO_PDL
     // Programmatic dependent launch: everything above touched only this CTA's shared and tensor
@@ -379,9 +388,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
         const int s = stage_of((int)(L / NC), (int)(L % NC));
         const long long row = first + (L / NC) * gridDim.x;
         const int c = (int)(L % NC);
-        if (lane == 0) mbar_arrive_expect_tx(bar(B_FULL + s), CH * G::ROW_BYTES);
+        const int valid = (K - c * CH < CH) ? K - c * CH : CH;     // channels of this chunk
+        if (lane == 0) mbar_arrive_expect_tx(bar(B_FULL + s), valid * G::ROW_BYTES);
         __syncwarp();
-        for (int j = lane; j < CH; j += 32) {
+        for (int j = lane; j < valid; j += 32) {
             const float2* src = p.x + row * p.x_stride_row + (long long)(c * CH + j) * p.x_stride_k;
             bulk_load(smem_u32(ring + s * G::STAGE_BYTES + j * G::ROW_STRIDE), src, G::ROW_BYTES, bar(B_FULL + s));
         }
@@ -424,9 +434,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) spectral_tc_kernel(const __grid
         tr_staged = clock64();
 #endif
         if (warp < kProducerWarp) {
-            for (int blk = share; blk < K / 4; blk += kConvShares) {
-                const float4 a = *reinterpret_cast<const float4*>(wst + n * wrow + blk * 32);
-                const float4 c = *reinterpret_cast<const float4*>(wst + n * wrow + blk * 32 + 16);
+            for (int blk = share; blk < Kp / 4; blk += kConvShares) {
+                const bool real = 4 * blk < K;                        // channels K .. Kp-1 get zero weights
+                const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 a = real ? *reinterpret_cast<const float4*>(wst + n * wrow + blk * 32) : zero4;
+                const float4 c = real ? *reinterpret_cast<const float4*>(wst + n * wrow + blk * 32 + 16) : zero4;
                 const float2 w4[4] = {make_float2(a.x, a.y), make_float2(a.z, a.w), make_float2(c.x, c.y), make_float2(c.z, c.w)};
                 uint32_t hi[8], lo[8];
 #pragma unroll
