@@ -92,7 +92,8 @@ def test_plan_reports_the_kernels_it_launches(cuda):
     assert kernels(1, 300, 256, 32, 128) == ["spectral_tc_kernel<8,1>"] * 2
     # everything else: the FP32 row-tile kernel
     assert kernels(1, 1, 128, 8, 64) == ["spectral_tile_kernel<2,1,1,1>"]
-    assert kernels(1, 5, 256, 32, 128) == ["spectral_tile_kernel<4,1,1,2>"]
+    assert kernels(1, 5, 256, 32, 128) == ["spectral_tile_kernel<4,1,1,1>"]       # small batch: grid over blocks of 64 outputs
+    assert kernels(1, 100, 256, 32, 128) == ["spectral_tile_kernel<4,1,1,2>"]     # 128 outputs per CTA
     assert kernels(1, 300, 256, 24, 64) == ["spectral_tc_kernel<8,1>"]                                 # 16 + 8 channels, padded chunk
     assert kernels(1, 100, 256, 24, 64) == ["spectral_tile_kernel<4,1,1,1>"]                           # ... not below a row per SM
     assert kernels(1, 300, 256, 128, 64) == ["spectral_tc_kernel<8,1>", "spectral_tc_kernel<8,1>+="]    # 64 + 64 channels

@@ -124,7 +124,7 @@ inline size_t tile_smem_bytes(int R, bool fwd, bool inv, int K, int N) {
 }
 
 template <int R, bool FWD, bool INV, int NB>
-inline int launch_tile_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
+inline int launch_tile_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st, int n_blocks = 1) {
     auto kernel = spectral_tile_kernel<R, FWD, INV, NB>;
     size_t smem = tile_smem_bytes(R, FWD, INV, p.K, p.N);
     if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
@@ -134,17 +134,17 @@ inline int launch_tile_inst(const DeviceInfo& dev, const TileParams& p, cudaStre
     if (rc != TFNO_OK) return rc;
     long long grid = (long long)dev.sms * occ;
     if (grid > p.rows) grid = p.rows;
-    kernel<<<(unsigned)grid, kThreads, smem, st>>>(p);
+    kernel<<<dim3((unsigned)grid, (unsigned)n_blocks), kThreads, smem, st>>>(p);    // p.N channels per block of blockIdx.y
     return launch_status();
 }
 
 template <bool FWD, bool INV, int NB>
-inline int launch_tile_r(const DeviceInfo& dev, int R, const TileParams& p, cudaStream_t st) {
+inline int launch_tile_r(const DeviceInfo& dev, int R, const TileParams& p, cudaStream_t st, int n_blocks = 1) {
     switch (R) {
-        case 2: return launch_tile_inst<2, FWD, INV, NB>(dev, p, st);
-        case 4: return launch_tile_inst<4, FWD, INV, NB>(dev, p, st);
-        case 8: return launch_tile_inst<8, FWD, INV, NB>(dev, p, st);
-        case 16: return launch_tile_inst<16, FWD, INV, NB>(dev, p, st);
+        case 2: return launch_tile_inst<2, FWD, INV, NB>(dev, p, st, n_blocks);
+        case 4: return launch_tile_inst<4, FWD, INV, NB>(dev, p, st, n_blocks);
+        case 8: return launch_tile_inst<8, FWD, INV, NB>(dev, p, st, n_blocks);
+        case 16: return launch_tile_inst<16, FWD, INV, NB>(dev, p, st, n_blocks);
     }
     return TFNO_ERR_UNSUPPORTED;
 }
@@ -377,6 +377,14 @@ inline int launch_tile(const DeviceInfo& dev, int len, TileParams p, cudaStream_
     }
     const int N = p.N;
     const long long M = p.rows * kModes;
+    // A wide layer on a small batch: one launch whose grid also runs over blocks of 64 output
+    // channels, so that the few rows are spread over N/64 times as many CTAs (a CTA that produces
+    // all 128 channels of its row takes 47 us at K = N = 128; the latency, not the work, counts).
+    if (N > 64 && p.rows * ((N + 127) / 128) * 2 <= dev.sms) {
+        TileParams q = p;
+        q.N = 64;
+        return launch_tile_r<FWD, INV, 1>(dev, R, q, st, N / 64);
+    }
     for (int n0 = 0; n0 < N; n0 += 128) {
         TileParams q = p;
         q.N = (N - n0 >= 128) ? 128 : 64;

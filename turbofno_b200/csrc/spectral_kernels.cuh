@@ -144,6 +144,10 @@ __global__ void __launch_bounds__(kThreads, 1) spectral_tile_kernel(TileParams p
 
     const long long M = p.rows * kModes;
     const int tm = tid & 15, tn = tid >> 4;        // GEMM thread tile: modes {2tm,2tm+1,32+2tm,33+2tm} x 4 n
+    // blockIdx.y selects a block of N output channels: small batches of a wide layer are spread
+    // over more CTAs that way (each repeats the row's forward transform, in parallel)
+    const float2* wbase = p.w + (long long)blockIdx.y * N * p.w_stride_n;
+    float2* ybase = p.y + (long long)blockIdx.y * N * (INV ? p.y_stride_n : M);
 
     for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
         // ---------------- stage 1: spectrum tile sA[k][m] ----------------
@@ -188,7 +192,7 @@ __global__ void __launch_bounds__(kThreads, 1) spectral_tile_kernel(TileParams p
                 int e = tid + i * kThreads;
                 int kk, n;
                 if (p.w_stride_n == 1) { n = e % N; kk = e / N; } else { kk = e % kSlabK; n = e / kSlabK; }
-                wreg[i] = __ldg(p.w + (long long)(k0 + kk) * p.w_stride_k + (long long)n * p.w_stride_n);
+                wreg[i] = __ldg(wbase + (long long)(k0 + kk) * p.w_stride_k + (long long)n * p.w_stride_n);
             }
         };
         auto stash_slab = [&](int buf) {
@@ -263,7 +267,7 @@ __global__ void __launch_bounds__(kThreads, 1) spectral_tile_kernel(TileParams p
                     }
                     if (p.conj_inverse) inverse_pad_lane<+1, R>(v, twI, j1);
                     else inverse_pad_lane<-1, R>(v, twI, j1);
-                    store_decimated_paired<R>(v, p.y + row * p.y_stride_row + (long long)n * p.y_stride_n, j1);   // whole warps: N is a multiple of 64
+                    store_decimated_paired<R>(v, ybase + row * p.y_stride_row + (long long)n * p.y_stride_n, j1);   // whole warps: N is a multiple of 64
                 }
             }
             __syncthreads();   // sC and sA are rewritten by the next row
@@ -274,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1) spectral_tile_kernel(TileParams p
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int n = 64 * b + 4 * tn + j;
-                    float2* dst = p.y + row * kModes + (long long)n * M;
+                    float2* dst = ybase + row * kModes + (long long)n * M;
                     float2 o[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) o[i] = cmul(acc[b][i][j], p.alpha);
