@@ -92,6 +92,24 @@ def test_cgemm_beta_zero_takes_the_tensor_core_kernel(cuda, rows, K):
     assert_close(C2.cpu().numpy(), ref, "cgemm (FP32 kernel)")
 
 
+def test_cgemm_wide_layer_runs_the_tensor_core_kernel_per_block_of_64_outputs(cuda):
+    import torch
+    import turbofno_b200 as t
+
+    rows, K, N = 600, 32, 192
+    M = rows * 64
+    rng = np.random.default_rng(77)
+    A = (rng.uniform(-1, 1, (K, M)) + 1j * rng.uniform(-1, 1, (K, M))).astype(np.complex64)
+    Bm = ((rng.standard_normal((N, K)) + 1j * rng.standard_normal((N, K))) / np.sqrt(K)).astype(np.complex64)
+    C = torch.full((N, M), float("nan"), dtype=torch.complex64, device=cuda)
+    t.cgemm(M, N, K, _dev(cuda, A), _dev(cuda, Bm), C, 1.0, 0.0)
+    assert_close(C.cpu().numpy(), Bm.astype(np.complex128) @ A.astype(np.complex128), "cgemm N=192 (tensor cores)")
+    # the 2D layer with 128 output channels: the plan reports two launches of the contraction
+    plan = t.SpectralConv(2, 8, 128, 32, 128, DX=128, variant="D")
+    assert plan.kernels().count("cgemm_tc_kernel<128>") == 2
+    plan.close()
+
+
 @pytest.mark.parametrize("DY", [128, 256])
 def test_partial_fusions(cuda, DY):
     import torch

@@ -302,10 +302,13 @@ inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream
     return launch_status();
 }
 
-// Tensor-core contraction of compact spectra: N = 64, K a multiple of 16 up to 64, beta = 0.
+// Tensor-core contraction of compact spectra: N a multiple of 64 (64 per launch), K a multiple of 16 up to 64, beta = 0.
 inline bool cgemm_tc_eligible(const DeviceInfo& dev, const TileParams& p) {
     if (!dev.use_tensor_cores || !dev.status) return false;
-    if (p.N != 64 || p.K < tcg::kCH || p.K > 64 || p.K % tcg::kCH != 0) return false;
+    if (p.N % 64 != 0 || p.K < tcg::kCH || p.K > 64 || p.K % tcg::kCH != 0) return false;
+    // wider than 64 output channels: one launch per block of 64, each re-reading the spectra --
+    // worth it only when the launches are long
+    if (p.N > 64 && p.rows < 2LL * dev.sms) return false;
     if (p.beta.x != 0.f || p.beta.y != 0.f) return false;
     return ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.y)) & 15) == 0;
 }
@@ -332,8 +335,16 @@ inline int launch_cgemm_tc_inst(const DeviceInfo& dev, const TileParams& p, cuda
 }
 // 128-mode tiles when M allows it and there are enough of them to fill the device
 inline int launch_cgemm_tc(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
-    if (p.rows % 2 == 0 && p.rows / 2 >= dev.sms) return launch_cgemm_tc_inst<128>(dev, p, st);
-    return launch_cgemm_tc_inst<64>(dev, p, st);
+    const long long M = p.rows * kModes;
+    for (int n0 = 0; n0 < p.N; n0 += 64) {
+        TileParams q = p;
+        q.N = 64;
+        q.w = p.w + (long long)n0 * p.w_stride_n;
+        q.y = p.y + (long long)n0 * M;
+        const int rc = (p.rows % 2 == 0 && p.rows / 2 >= dev.sms) ? launch_cgemm_tc_inst<128>(dev, q, st) : launch_cgemm_tc_inst<64>(dev, q, st);
+        if (rc != TFNO_OK) return rc;
+    }
+    return TFNO_OK;
 }
 
 // Row-tile kernel for any N that is a multiple of 64: output channels are processed in blocks of
