@@ -2,11 +2,14 @@
 // tensor cores (tcgen05 + TMEM) and bulk-copy (TMA engine) staging of input and output rows.
 // Same operator as spectral_tile_kernel<R,true,true,1>
 // (fusion_variants/1D_D_exp_fused_fft_cgemm_ifft/fused_fft_cgemm_ifft_7.cuh:9-222 in the
-// reference), restricted to N = 64 output channels, K <= 96, DY in {128, 256, 512, 1024}.
+// reference), restricted to N = 64 output channels, K a multiple of 4 up to 96 (the launcher sends
+// multiples of 8; a last chunk of fewer than CH channels gets zero weights), DY in {128, 256,
+// 512, 1024}.  With `accumulate` the result is ADDED to y (the copy engine's reduce-add): the
+// launcher covers K up to 192 with two launches over the halves of the channels.
 //
 // One persistent CTA per SM, 768 threads in six warpgroups.  The transforms run on the 32-point
 // register FFT (fft32.cuh): a signal is spread over R = DY/32 lanes, a thread holds 32 samples, so
-// a compute thread needs ~110 registers and FOUR compute warps share a scheduler (the earlier
+// a compute thread needs 104 registers and FOUR compute warps share a scheduler (the earlier
 // 64-point design had two at 216 registers and was bound by exposed latency: issue slots 37 % used).
 // setmaxnreg moves registers from the two helper warpgroups to the four compute warpgroups.
 //
@@ -18,9 +21,11 @@
 //                             stores them as the B operand S[mode][kk] (K-major core matrices) in
 //                             the half-team's own S buffer.
 //   warps 1,3,..,15  inverse  groups of R lanes read one output channel's 64 modes from the Re/Im
-//                             planes and run the zero-padded inverse transform; at DY = 256 the
-//                             rows are staged in shared memory and leave by cp.async.bulk, at
-//                             DY = 128 the lanes store directly.
+//                             planes and run the zero-padded inverse transform; from DY = 256 up
+//                             the rows are staged in shared memory and leave through the copy
+//                             engine (DY = 256: the four rows of a task as one tiled copy over a
+//                             tensor map of y), at DY = 128 the lanes store directly.  The inverse
+//                             tasks of a CTA's LAST row are shared with the forward warps.
 //   warps 16-19      hand-off tcgen05.ld of one accumulator row per thread -> Re/Im planes in
 //                             shared memory (a warp may only touch its own quarter of tensor
 //                             memory, so this needs four warps with distinct warp%4).
