@@ -43,7 +43,9 @@ def test_operator_has_no_cpu_kernel():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("B,K,N,DY", [(5, 16, 64, 256), (3, 8, 128, 128), (150, 64, 64, 256)])
+@pytest.mark.parametrize("B,K,N,DY", [(5, 16, 64, 256), (3, 8, 128, 128), (150, 64, 64, 256),
+                                        # batch-first strides through the padded-chunk and the two-launch paths of the fused kernel
+                                        (300, 24, 64, 256), (300, 128, 64, 256), (300, 104, 128, 128)])
 def test_spectral_conv1d_operator(cuda, B, K, N, DY):
     import torch
 
