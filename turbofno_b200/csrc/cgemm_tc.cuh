@@ -48,6 +48,7 @@ struct CgemmTcParams {
     const float2* w; long long w_stride_k, w_stride_n;
     float2* c; long long c_stride_n;             // C[m + n * c_stride_n]
     float2 alpha;
+    int accumulate;                      // 1: C += alpha A W (the second of two launches over the halves of K > 64)
     int* status;
 };
 
@@ -70,8 +71,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) cgemm_tc_kernel(CgemmTcParams
     constexpr int kRowBytes = GemmGeom<TN>::ROW_BYTES, kRowStride = GemmGeom<TN>::ROW_STRIDE, kStageBytes = GemmGeom<TN>::STAGE_BYTES;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int K = p.K;
-    const int NC = K / CH;                        // chunks per tile
+    const int K = p.K;                            // a multiple of 8
+    const int NC = (K + CH - 1) / CH;             // chunks per tile; a last chunk of 8 channels is padded:
+    const int Kp = NC * CH;                       // zero weights, and ring rows no copy writes are zeroed once
     const int SBO = s_sbo(R), SBYTES = (TN / 8) * SBO;            // hi or lo array of one chunk buffer
     unsigned char* ring = base;
     unsigned char* sS = ring + kGemmStages * kStageBytes;           // [buffer 0: hi | lo][buffer 1: hi | lo]
@@ -102,11 +104,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) cgemm_tc_kernel(CgemmTcParams
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (Kp != K) {
+        for (int i = tid; i < kGemmStages * kStageBytes / 16; i += kGemmThreads) reinterpret_cast<uint4*>(ring)[i] = make_uint4(0u, 0u, 0u, 0u);
+        fence_async_smem();                       // before the copy engine writes other rows of the same stages
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t TM_WHI = 0, TM_WLO = 2 * K, TM_ACC = 4 * K;
+    const uint32_t TM_WHI = 0, TM_WLO = 2 * Kp, TM_ACC = 4 * Kp;
 
     const long long first = blockIdx.x;
     const int n_it = first < p.tiles ? (int)((p.tiles - first + gridDim.x - 1) / gridDim.x) : 0;
@@ -136,12 +142,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) cgemm_tc_kernel(CgemmTcParams
         if (warp < 12) {
             const int i = 32 * (warp & 3) + lane, n = i & 63, im_row = i >> 6;
             const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-            for (int blk = warp >> 2; blk < K / 8; blk += 3) {      // eight channels c*CH + k0 .. +7
+            for (int blk = warp >> 2; blk < Kp / 8; blk += 3) {     // eight channels c*CH + k0 .. +7
                 const int c = (8 * blk) / CH, k0 = (8 * blk) % CH;
+                const bool real = 8 * blk < K;                       // channels K .. Kp-1 get zero weights
                 float2 wv[8];
 #pragma unroll
                 for (int j = 0; j < 8; j += 2) {
-                    const float4 t = *reinterpret_cast<const float4*>(wst + n * wrow + (8 * blk + j) * 8);
+                    const float4 t = real ? *reinterpret_cast<const float4*>(wst + n * wrow + (8 * blk + j) * 8) : make_float4(0.f, 0.f, 0.f, 0.f);
                     wv[j] = cmul(make_float2(t.x, t.y), p.alpha);
                     wv[j + 1] = cmul(make_float2(t.z, t.w), p.alpha);
                 }
@@ -206,9 +213,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) cgemm_tc_kernel(CgemmTcParams
                 const int s = h + 2 * (int)(j & 1);
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(B_EMPTY + s), ((j >> 1) & 1) ^ 1, abort_flag, p.status, 73, kHelperIdleNs));
                 if (!ok) break;
-                if (lane == 0) mbar_arrive_expect_tx(bar(B_FULL + s), CH * kRowBytes);
+                const int valid = (K - c * CH < CH) ? K - c * CH : CH;      // channels of this chunk
+                if (lane == 0) mbar_arrive_expect_tx(bar(B_FULL + s), valid * kRowBytes);
                 __syncwarp();
-                if (lane < CH) {
+                if (lane < valid) {
                     const float2* src = p.a + (long long)(c * CH + lane) * p.a_stride_k + tile * TN;
                     bulk_load(smem_u32(ring + s * kStageBytes + lane * kRowStride), src, kRowBytes, bar(B_FULL + s));
                 }
@@ -312,7 +320,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) cgemm_tc_kernel(CgemmTcParams
                     const int off = n * TN + plane_chunk(n, 16 * pq + (lane >> 1)) * 4 + (lane & 1) * 2;
                     const float2 re = *reinterpret_cast<const float2*>(planes + off);
                     const float2 im = *reinterpret_cast<const float2*>(planes + 64 * TN + off);
-                    *reinterpret_cast<float4*>(crow + 64 * pq + 2 * lane) = make_float4(re.x, im.x, re.y, im.y);
+                    float4 o = make_float4(re.x, im.x, re.y, im.y);
+                    if (p.accumulate) {
+                        const float4 prev = *reinterpret_cast<const float4*>(crow + 64 * pq + 2 * lane);
+                        o.x += prev.x; o.y += prev.y; o.z += prev.z; o.w += prev.w;
+                    }
+                    *reinterpret_cast<float4*>(crow + 64 * pq + 2 * lane) = o;
                 }
             }
             // release orders this lane's plane reads before the arrive, __syncwarp those of the others

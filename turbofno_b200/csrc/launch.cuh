@@ -305,19 +305,21 @@ inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream
 // Tensor-core contraction of compact spectra: N a multiple of 64 (64 per launch), K a multiple of 16 up to 64, beta = 0.
 inline bool cgemm_tc_eligible(const DeviceInfo& dev, const TileParams& p) {
     if (!dev.use_tensor_cores || !dev.status) return false;
-    if (p.N % 64 != 0 || p.K < tcg::kCH || p.K > 64 || p.K % tcg::kCH != 0) return false;
-    // wider than 64 output channels: one launch per block of 64, each re-reading the spectra --
-    // worth it only when the launches are long
-    if (p.N > 64 && p.rows < 2LL * dev.sms) return false;
+    // K a multiple of 8 (a last chunk of 8 channels is padded with zero weights), at most 64 per
+    // launch (tensor memory) and 128 in two launches, the second adding to C
+    if (p.N % 64 != 0 || p.K < 8 || p.K > 128 || p.K % 8 != 0) return false;
+    // several launches (per block of 64 output channels, per half of K > 64), each re-reading its
+    // spectra: worth it only when the launches are long
+    if ((p.N > 64 || p.K > 64) && p.rows < 2LL * dev.sms) return false;
     if (p.beta.x != 0.f || p.beta.y != 0.f) return false;
     return ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.y)) & 15) == 0;
 }
 template <int TN>
-inline int launch_cgemm_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
+inline int launch_cgemm_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream_t st, bool accumulate) {
     auto kernel = tcg::cgemm_tc_kernel<TN>;
     const size_t smem = tcg::cgemm_tc_smem_bytes<TN>();
     if ((long long)smem > dev.max_smem_optin) return TFNO_ERR_UNSUPPORTED;
-    if (record_launch(dev, "cgemm_tc_kernel<%d>", TN)) return TFNO_OK;
+    if (record_launch(dev, accumulate ? "cgemm_tc_kernel<%d>+=" : "cgemm_tc_kernel<%d>", TN)) return TFNO_OK;
     int occ = 0;
     int rc = prepare_kernel(kernel, smem, dev, &occ, tcg::kGemmThreads);
     if (rc != TFNO_OK) return rc;
@@ -328,6 +330,7 @@ inline int launch_cgemm_tc_inst(const DeviceInfo& dev, const TileParams& p, cuda
     q.w = p.w; q.w_stride_k = p.w_stride_k; q.w_stride_n = p.w_stride_n;
     q.c = p.y; q.c_stride_n = M;
     q.alpha = p.alpha; q.status = dev.status;
+    q.accumulate = accumulate ? 1 : 0;
     long long grid = dev.sms;
     if (grid > q.tiles) grid = q.tiles;
     kernel<<<(unsigned)grid, tcg::kGemmThreads, smem, st>>>(q);
@@ -336,13 +339,19 @@ inline int launch_cgemm_tc_inst(const DeviceInfo& dev, const TileParams& p, cuda
 // 128-mode tiles when M allows it and there are enough of them to fill the device
 inline int launch_cgemm_tc(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
     const long long M = p.rows * kModes;
+    const int K1 = p.K <= 64 ? p.K : ((p.K / 2 + tcg::kCH - 1) / tcg::kCH) * tcg::kCH;     // channels of the first launch
     for (int n0 = 0; n0 < p.N; n0 += 64) {
-        TileParams q = p;
-        q.N = 64;
-        q.w = p.w + (long long)n0 * p.w_stride_n;
-        q.y = p.y + (long long)n0 * M;
-        const int rc = (p.rows % 2 == 0 && p.rows / 2 >= dev.sms) ? launch_cgemm_tc_inst<128>(dev, q, st) : launch_cgemm_tc_inst<64>(dev, q, st);
-        if (rc != TFNO_OK) return rc;
+        for (int k0 = 0; k0 < p.K; k0 += K1) {
+            TileParams q = p;
+            q.N = 64;
+            q.K = (k0 == 0) ? K1 : p.K - K1;
+            q.x = p.x + (long long)k0 * M;                   // A[m + k*M]
+            q.w = p.w + (long long)n0 * p.w_stride_n + (long long)k0 * p.w_stride_k;
+            q.y = p.y + (long long)n0 * M;
+            const bool acc = k0 != 0;
+            const int rc = (p.rows % 2 == 0 && p.rows / 2 >= dev.sms) ? launch_cgemm_tc_inst<128>(dev, q, st, acc) : launch_cgemm_tc_inst<64>(dev, q, st, acc);
+            if (rc != TFNO_OK) return rc;
+        }
     }
     return TFNO_OK;
 }
