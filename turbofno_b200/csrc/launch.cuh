@@ -311,6 +311,9 @@ inline bool cgemm_tc_eligible(const DeviceInfo& dev, const TileParams& p) {
     // several launches (per block of 64 output channels, per half of K > 64), each re-reading its
     // spectra: worth it only when the launches are long
     if ((p.N > 64 || p.K > 64) && p.rows < 2LL * dev.sms) return false;
+    // two launches re-read the spectra and read C once more: measured slower than the FP32 kernel at
+    // K = 72 (2D, bs = 64..128: +4 %), faster at K = 128 (-5 to -11 %)
+    if (p.K > 64 && p.K < 96) return false;
     if (p.beta.x != 0.f || p.beta.y != 0.f) return false;
     return ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.y)) & 15) == 0;
 }
