@@ -112,6 +112,6 @@ def test_plan_reports_the_kernels_it_launches(cuda):
     assert kernels(2, 1, 128, 8, 64, DX=128) == ["fft2d_trunc_kernel<2,2,paired,128>", "cgemm_tc_kernel<64>", "ifft2d_pad_kernel<2,2,paired,128>"]
     assert kernels(2, 8, 128, 104, 64, DX=128)[1:3] == ["cgemm_tc_kernel<128>", "cgemm_tc_kernel<128>+="]     # 64 + 40 channels
     assert kernels(2, 1, 128, 104, 64, DX=128)[1] == "spectral_tile_kernel<2,0,0,1>"                         # too few rows for two launches
-    assert kernels(2, 8, 128, 72, 64, DX=128)[1] == "spectral_tile_kernel<2,0,0,1>"                          # 65..95 channels: FP32 is faster
+    assert kernels(2, 8, 128, 72, 64, DX=128)[1] == "cgemm_tc_kernel<64>"                                    # 65..96 channels: 64-mode tiles
     # library path
     assert kernels(1, 4, 128, 8, 64, "E") == ["cufftExecC2C", "truncate_rows_kernel", "cublasCgemm", "zero_pad_rows_kernel", "cufftExecC2C"]

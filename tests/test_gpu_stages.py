@@ -66,10 +66,10 @@ def test_cgemm(cuda, rows, K, N):
 
 @pytest.mark.parametrize("rows,K", [(1, 16), (7, 32), (149, 48), (600, 64), (296, 16), (1000, 48),
                                      # a padded last chunk (8 of 16 channels), and two launches over the halves of K > 64
-                                     (5, 8), (301, 24), (600, 56), (600, 104), (298, 128), (1001, 120)])
+                                     (5, 8), (301, 24), (600, 56), (600, 72), (297, 96), (600, 104), (298, 128), (1001, 120)])
 def test_cgemm_beta_zero_takes_the_tensor_core_kernel(cuda, rows, K):
-    """beta = 0, K a multiple of 8 up to 64 or from 96 to 128: the contraction runs on tcgen05
-    (cgemm_tc_kernel; K > 64 needs two rows of tiles per SM), every other case on the FP32 kernel; both must agree with the
+    """beta = 0, K a multiple of 8 up to 128: the contraction runs on tcgen05 (cgemm_tc_kernel; K > 64
+    needs two rows of tiles per SM), every other case on the FP32 kernel; both must agree with the
     float64 product. Even row counts of at
     least two per SM use 128-mode tiles, the others 64-mode tiles. 149 and 600 tiles give
     the CTAs of a 148-SM device one, two and five tiles (double-buffered accumulators, both ring

@@ -127,7 +127,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) cgemm_tc_kernel(CgemmTcParams
     // into the S buffers and planes, which nothing uses yet, as [n][K channels + 16 bytes], and warps
     // 0-11 (three per TMEM quarter) convert from there.
     {
-        static_assert(2 * 2 * (TN / 8) * s_sbo(4) + 2 * 64 * TN * 4 >= 64 * (64 * 8 + 16), "weight staging area (K <= 64)");
+        // K <= 64 with 128-mode tiles, K <= 96 with 64-mode tiles (tensor memory: 4K + 2 TN <= 512 columns)
+        static_assert(2 * 2 * (TN / 8) * s_sbo(4) + 2 * 64 * TN * 4 >= 64 * ((TN == 64 ? 96 : 64) * 8 + 16), "weight staging area");
         unsigned char* wst = sS;
         const int wrow = K * 8 + 16;
         const bool k_fast = p.w_stride_k == 1;

@@ -305,15 +305,13 @@ inline int launch_tc_inst(const DeviceInfo& dev, const TileParams& p, cudaStream
 // Tensor-core contraction of compact spectra: N a multiple of 64 (64 per launch), K a multiple of 16 up to 64, beta = 0.
 inline bool cgemm_tc_eligible(const DeviceInfo& dev, const TileParams& p) {
     if (!dev.use_tensor_cores || !dev.status) return false;
-    // K a multiple of 8 (a last chunk of 8 channels is padded with zero weights), at most 64 per
+    // K a multiple of 8 (a last chunk of 8 channels is padded with zero weights), at most 96 per
     // launch (tensor memory) and 128 in two launches, the second adding to C
     if (p.N % 64 != 0 || p.K < 8 || p.K > 128 || p.K % 8 != 0) return false;
     // several launches (per block of 64 output channels, per half of K > 64), each re-reading its
     // spectra: worth it only when the launches are long
     if ((p.N > 64 || p.K > 64) && p.rows < 2LL * dev.sms) return false;
-    // two launches re-read the spectra and read C once more: measured slower than the FP32 kernel at
-    // K = 72 (2D, bs = 64..128: +4 %), faster at K = 128 (-5 to -11 %)
-    if (p.K > 64 && p.K < 96) return false;
+
     if (p.beta.x != 0.f || p.beta.y != 0.f) return false;
     return ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.y)) & 15) == 0;
 }
@@ -342,7 +340,10 @@ inline int launch_cgemm_tc_inst(const DeviceInfo& dev, const TileParams& p, cuda
 // 128-mode tiles when M allows it and there are enough of them to fill the device
 inline int launch_cgemm_tc(const DeviceInfo& dev, const TileParams& p, cudaStream_t st) {
     const long long M = p.rows * kModes;
-    const int K1 = p.K <= 64 ? p.K : ((p.K / 2 + tcg::kCH - 1) / tcg::kCH) * tcg::kCH;     // channels of the first launch
+    // 65..96 channels: one launch on 64-mode tiles, whose smaller accumulators leave room for the
+    // weights in tensor memory (4K + 2 TN <= 512 columns); more: two launches over the halves
+    const bool narrow = p.K > 64 && p.K <= 96;
+    const int K1 = p.K <= 96 ? p.K : ((p.K / 2 + tcg::kCH - 1) / tcg::kCH) * tcg::kCH;     // channels of the first launch
     for (int n0 = 0; n0 < p.N; n0 += 64) {
         for (int k0 = 0; k0 < p.K; k0 += K1) {
             TileParams q = p;
@@ -352,7 +353,7 @@ inline int launch_cgemm_tc(const DeviceInfo& dev, const TileParams& p, cudaStrea
             q.w = p.w + (long long)n0 * p.w_stride_n + (long long)k0 * p.w_stride_k;
             q.y = p.y + (long long)n0 * M;
             const bool acc = k0 != 0;
-            const int rc = (p.rows % 2 == 0 && p.rows / 2 >= dev.sms) ? launch_cgemm_tc_inst<128>(dev, q, st, acc) : launch_cgemm_tc_inst<64>(dev, q, st, acc);
+            const int rc = (!narrow && p.rows % 2 == 0 && p.rows / 2 >= dev.sms) ? launch_cgemm_tc_inst<128>(dev, q, st, acc) : launch_cgemm_tc_inst<64>(dev, q, st, acc);
             if (rc != TFNO_OK) return rc;
         }
     }
